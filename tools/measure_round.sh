@@ -16,5 +16,5 @@ timeout 120 python tools_trace.py 7b 2048 > $o/m_trace_7b_q4_0.txt 2>&1
 timeout 300 python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-sub-records > /dev/null 2>&1 && \
   timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -c 400 --csv --log-file $o/m_decode_launches.csv python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-sub-records > $o/m_ncu_launch.log 2>&1
 timeout 300 python tools/run_fused.py 6 > $o/m_plain.log 2>&1 && \
-  timeout 900 ncu --set full --clock-control none --import-source on -k regex:decoder_kernel -s 3 -c 1 -o $o/m_decode_full -f python tools/run_fused.py 6 > $o/m_ncu_full.log 2>&1
+  timeout 900 ncu --set full --clock-control none -k regex:decoder_kernel -s 3 -c 1 -o $o/m_decode_full -f python tools/run_fused.py 6 > $o/m_ncu_full.log 2>&1
 for f in $o/m_bench_*.json; do python -c "import json,sys; d=json.load(open('$f')); print('$f', d.get('value'), d.get('ms_per_step'), (d.get('roofline') or {}).get('frac'), (d.get('e2e') or {}).get('value'))"; done
