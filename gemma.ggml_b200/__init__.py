@@ -22,6 +22,8 @@ HEADER = os.path.join(ROOT, "include", "ggml_b200.h")
 
 TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
 TYPE_Q4_K, TYPE_Q6_K, TYPE_Q8_K = 12, 14, 15
+TYPE_BF16 = 30
+DTYPES = {"bfloat16": TYPE_BF16, "float32": TYPE_F32}
 BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34}
 
 
@@ -124,6 +126,25 @@ _CUDA_SIG = {
     "ggb_decoder_stream_bytes": (C.c_longlong, [vp]), "ggb_decoder_kv_heads": (i32, [vp]),
     "ggb_decoder_free": (i32, [vp]), "ggb_decoder_trace": (i32, [vp, vp, vp, i32, P(i32), P(i32)]),
     "ggb_decoder_exp_computed": (i32, [vp]),
+    "ggb_dtype_size": (sz, [i32]),
+    "ggb_op_linear": (i32, [i32, vp, i64, i64, vp, i64, i64, vp, i64]),
+    "ggb_op_rms_norm2": (i32, [i32, vp, i64, vp, i32, vp, i32, f32, i64, i64, vp, vp]),
+    "ggb_op_gather_rows_f32": (i32, [vp, vp, i64, i64, vp]),
+    "ggb_op_embed_rows": (i32, [i32, vp, vp, i64, i64, vp]),
+    "ggb_op_glu_clamp": (i32, [i32, vp, i64, i64, f32, f32, vp]),
+    "ggb_op_residual_side": (i32, [i32, vp, vp, vp, i64, i64, vp, vp, i64, i64, i32, vp, vp, vp, f32]),
+    "ggb_op_cvt_bf16_f32": (i32, [vp, i64, vp]),
+    "ggb_latent_cache_ld": (i64, [i32, i32]),
+    "ggb_op_latent_kv_store": (i32, [i32, vp, i64, i64, i32, i32, i32, vp, f32, vp, vp, vp, i32, vp]),
+    "ggb_op_latent_q_absorb": (i32, [i32, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, i32, f32, vp]),
+    "ggb_latent_attn_scratch_bytes": (sz, [i64, i32, i32, i32]),
+    "ggb_op_latent_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, vp]),
+    "ggb_op_latent_attn_out": (i32, [i32, vp, i32, vp, vp, i64, i32, i32, i32, vp]),
+    "ggb_op_moe_route": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp]),
+    "ggb_moe_max_tiles": (i32, [i64, i32]), "ggb_moe_group_ints": (sz, [i64, i32]),
+    "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),
+    "ggb_op_moe_linear": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, vp, i32, vp, i64]),
+    "ggb_op_moe_combine": (i32, [vp, vp, vp, i64, i32, i32, i64, vp]),
     "ggb_comm_unique_id": (i32, [vp]), "ggb_comm_init": (i32, [vp, i32, i32]), "ggb_comm_destroy": (i32, []),
     "ggb_comm_rank": (i32, []), "ggb_comm_size": (i32, []), "ggb_op_allgather": (i32, [vp, vp, sz]),
 }
@@ -151,6 +172,15 @@ _HOST_SIG = {
     "td_dump_capture": (i32, [vp, C.c_char_p, i32, i64, i32]), "td_compare_tensors": (i32, [C.c_char_p]),
     "td_compare_tensors_report": (i32, [C.c_char_p, P(C.c_double)]),
     "gm_get_kv": (i32, [vp, i32, vp, vp]), "gm_kernels_per_step": (i32, [vp]), "gm_weight_bytes": (u64, [vp]),
+    "lm_engine_open": (vp, [C.c_char_p, C.c_char_p, i32, i64, i32, i32, i32, i32, u64]),
+    "lm_engine_close": (None, [vp]), "lm_engine_error": (C.c_char_p, [vp]), "lm_engine_vocab": (i32, [vp]),
+    "lm_engine_architecture": (C.c_char_p, [vp]),
+    "lm_engine_step": (i32, [vp, i32, P(C.c_char_p), P(vp), P(i32), P(vp), P(i32), i32, P(C.c_char_p), vp]),
+    "lm_engine_generate": (i32, [vp, C.c_char_p, vp, i32, i32, vp]),
+    "lm_engine_stats": (i32, [vp, P(i64)]), "lm_engine_seq_len": (i64, [vp, C.c_char_p]),
+    "lm_engine_seq_pages": (i32, [vp, C.c_char_p, vp, i32]),
+    "lm_engine_capture": (i32, [vp, i32]), "lm_engine_get_capture": (i32, [vp, i32, vp, i64]),
+    "lm_architectures_csv": (i32, [C.c_char_p, i32]),
     "mul_mat": (None, [i64, i64, i64, i64, i64, i64, i64, sz, i64, vp, vp, vp, vp, i32, vp]),
     "init_cuda_offload": (i32, [i32]),
 }
@@ -611,3 +641,96 @@ class GemmaModel:
     @property
     def weight_bytes(self):
         return int(self.H.gm_weight_bytes(self.h))
+
+
+def architectures():
+    """Architecture names the model registry knows (host/lm_model.h)."""
+    buf = C.create_string_buffer(1024)
+    host_lib().lm_architectures_csv(buf, 1024)
+    return [a for a in buf.value.decode().split(",") if a]
+
+
+class Engine:
+    """The serving engine (host/lm_engine.h) over a model chosen by config.json's "architecture": sequences by
+    name, a paged cache sized for max_tokens, steps of token portions, greedy generation.
+
+    Engine(model_dir) loads config.json + model.safetensors; Engine(config=dict, seed=...) builds the same
+    architecture with random weights (throughput runs, tests of other sizes)."""
+
+    def __init__(self, model_dir=None, dtype="bfloat16", max_tokens=4096, page_size=64, max_seqs=8, max_portion=0,
+                 config=None, seed=None):
+        import json
+        init()
+        dt = DTYPES[dtype] if isinstance(dtype, str) else int(dtype)
+        text = json.dumps(config).encode() if config is not None else None
+        self.h = host_lib().lm_engine_open(model_dir.encode() if model_dir else None, text, dt, int(max_tokens),
+                                           int(page_size), int(max_seqs), int(max_portion),
+                                           1 if (model_dir is None or seed is not None) else 0, int(seed or 0))
+        if not self.h:
+            raise GgbError("engine: " + host_lib().gm_last_error().decode(errors="replace"))
+        self.vocab = int(host_lib().lm_engine_vocab(self.h))
+        self.architecture = host_lib().lm_engine_architecture(self.h).decode()
+
+    def _check(self, rc, what):
+        if rc != 0:
+            raise GgbError(f"{what} failed (rc={rc}): {host_lib().lm_engine_error(self.h).decode(errors='replace')}")
+
+    def step(self, entries, end=()):
+        """entries: [(id, tokens, want)], end: ids that are finished after this step.  Returns the logits of the
+        wanted places, float32 [sum(len(want)), vocab], in the order of the entries and of their want lists."""
+        n = len(entries)
+        ids = (C.c_char_p * max(n, 1))(*[str(e[0]).encode() for e in entries])
+        toks = [np.ascontiguousarray(e[1], dtype=np.int32) for e in entries]
+        want = [np.ascontiguousarray(e[2], dtype=np.int32) for e in entries]
+        tp = (vp * max(n, 1))(*[_ptr(t) for t in toks])
+        wp = (vp * max(n, 1))(*[_ptr(w) for w in want])
+        nt = (i32 * max(n, 1))(*[len(t) for t in toks])
+        nw = (i32 * max(n, 1))(*[len(w) for w in want])
+        ends = (C.c_char_p * max(len(end), 1))(*[str(e).encode() for e in end])
+        out = np.empty((sum(len(w) for w in want), self.vocab), dtype=np.float32)
+        self._check(host_lib().lm_engine_step(self.h, n, ids, tp, nt, wp, nw, len(end), ends, _ptr(out)), "step")
+        return out
+
+    def generate(self, seq_id, prompt, n_new):
+        """Greedy continuation (first maximum) through the engine's own step function; the sequence stays live."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.empty(n_new, dtype=np.int32)
+        self._check(host_lib().lm_engine_generate(self.h, str(seq_id).encode(), _ptr(prompt), len(prompt), n_new, _ptr(out)),
+                    "generate")
+        return out
+
+    def end(self, *ids):
+        self.step([], ids)
+
+    def stats(self):
+        o = (i64 * 6)()
+        host_lib().lm_engine_stats(self.h, o)
+        return dict(zip(("live_seqs", "free_pages", "pages", "page_size", "kernels_last_forward", "weight_bytes"), list(o)))
+
+    def seq_len(self, seq_id):
+        return int(host_lib().lm_engine_seq_len(self.h, str(seq_id).encode()))
+
+    def seq_pages(self, seq_id):
+        buf = np.empty(self.stats()["pages"], dtype=np.int32)
+        n = host_lib().lm_engine_seq_pages(self.h, str(seq_id).encode(), _ptr(buf), len(buf))
+        return buf[:max(n, 0)].copy()
+
+    def capture(self, on=True):
+        self._check(host_lib().lm_engine_capture(self.h, 1 if on else 0), "capture")
+
+    def captured(self, layer, tokens, width):
+        """Residual stream after `layer` of the last forward call: float32 [tokens, width]."""
+        out = np.empty((tokens, width), dtype=np.float32)
+        self._check(host_lib().lm_engine_get_capture(self.h, layer, _ptr(out), out.size), "get_capture")
+        return out
+
+    def close(self):
+        if getattr(self, "h", None):
+            host_lib().lm_engine_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

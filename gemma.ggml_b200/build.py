@@ -8,6 +8,7 @@ Usage: python gemma.ggml_b200/build.py [--force]
 """
 import glob
 import os
+from concurrent.futures import ThreadPoolExecutor
 import subprocess
 import sys
 
@@ -59,22 +60,25 @@ def build(force=False, verbose=False):
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h")) + \
         glob.glob(os.path.join(HOST, "*.h")) + [os.path.abspath(__file__)]
     # ---- CUDA layer
-    objs = []
+    objs, jobs = [], []
     for src in sorted(glob.glob(os.path.join(CSRC, "*.cu"))):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
             extra = ["-Xptxas", "-v"] if verbose else []
-            _run([NVCC] + NVCC_FLAGS + extra + ["-I", NCCL_INC, "-c", src, "-o", obj])
-    if force or _stale(CUDA_LIB, objs):
-        _run([NVCC, "-shared", "-o", CUDA_LIB] + objs + ["-lcudart", "-ldl"])
+            jobs.append([NVCC] + NVCC_FLAGS + extra + ["-I", NCCL_INC, "-c", src, "-o", obj])
     # ---- host C++ layer
     hobjs = []
     for src in sorted(glob.glob(os.path.join(HOST, "*.cpp"))):
         obj = os.path.join(OBJ, "host_" + os.path.basename(src)[:-4] + ".o")
         hobjs.append(obj)
         if force or _stale(obj, [src] + headers):
-            _run([CXX] + CXX_FLAGS + ["-c", src, "-o", obj])
+            jobs.append([CXX] + CXX_FLAGS + ["-c", src, "-o", obj])
+    # every translation unit is independent: compile them side by side, then link the two libraries
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
+        list(pool.map(_run, jobs))
+    if force or _stale(CUDA_LIB, objs):
+        _run([NVCC, "-shared", "-o", CUDA_LIB] + objs + ["-lcudart", "-ldl"])
     if hobjs and (force or _stale(HOST_LIB, hobjs + [CUDA_LIB])):
         _run([CXX, "-shared", "-o", HOST_LIB] + hobjs +
              ["-L", HERE, "-lggb_cuda", "-Wl,-rpath,$ORIGIN", "-lpthread"])

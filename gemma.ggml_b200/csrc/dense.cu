@@ -1,0 +1,366 @@
+// dense.cu — operators for models whose matrices are plain bf16 / fp32 (row-major [out][in], applied as W x):
+// the linear layer in three forms (a streaming mat-vec for a handful of rows, a shared-memory tile kernel for any
+// shape, and - bf16, aligned shapes - the tcgen05 GEMM of prefill.cu), RMS norms whose weight is one number or a
+// vector, the clamped gated activation, embedding rows, and the residual sum with a per-token side input.
+//
+// `dt` is the storage type of matrices and of the activations that feed them: GGB_TYPE_BF16 (products of bf16
+// values accumulated in fp32) or GGB_TYPE_F32 (everything in true fp32; no TF32 anywhere).  Norms, the residual
+// stream and every reduction are fp32 in both.  The file is compiled with -fmad=false, so the fused multiply-adds
+// are spelled fmaf().
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "dense.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------ mat-vec
+// T <= kVecT activation rows: a warp owns output row n for all of them, streams the weight row once with
+// 16-byte loads and keeps T accumulators.  HBM-bound (decode).
+constexpr int kVecT = 8;
+
+template <typename E, int TT>
+__global__ void __launch_bounds__(256) linear_vec_kernel(const E *__restrict__ w, int64_t N, int64_t K, const E *__restrict__ a,
+                                                         int64_t lda, float *__restrict__ c, int64_t ldc) {
+    constexpr int VE = 16 / (int)sizeof(E); // elements per 16-byte load
+    const int lane = threadIdx.x & 31;
+    const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) acc[t] = 0.f;
+    const E *wr = w + n * K;
+    const bool vec = (K % VE == 0) && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(a)) % 16 == 0) &&
+                     (lda % VE == 0);
+    if (vec) {
+        for (int64_t k = (int64_t)lane * VE; k < K; k += 32 * VE) {
+            const uint4 wv = ldg_stream_u4(wr + k);
+            const E *we = reinterpret_cast<const E *>(&wv);
+            float wf[VE];
+#pragma unroll
+            for (int u = 0; u < VE; u++) wf[u] = to_f32(we[u]);
+#pragma unroll
+            for (int t = 0; t < TT; t++) {
+                const uint4 av = *reinterpret_cast<const uint4 *>(a + t * lda + k);
+                const E *ae = reinterpret_cast<const E *>(&av);
+#pragma unroll
+                for (int u = 0; u < VE; u++) acc[t] = fmaf(wf[u], to_f32(ae[u]), acc[t]);
+            }
+        }
+    } else {
+        for (int64_t k = lane; k < K; k += 32) {
+            const float wf = to_f32(wr[k]);
+#pragma unroll
+            for (int t = 0; t < TT; t++) acc[t] = fmaf(wf, to_f32(a[t * lda + k]), acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        const float s = warp_sum_f32(acc[t]);
+        if (lane == 0) c[t * ldc + n] = s;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ tile kernel
+// C[T][N] = A[T][K] W[N][K]^T for any shape: 64 x 64 tile of C per CTA, K in steps of 16, 4 x 4 outputs per
+// thread, fp32 accumulation in k order.  With `grp` the rows of A / C are the sorted slots of a mixture of experts:
+// tile blockIdx.y belongs to expert grp.tile_expert[y], covers sorted rows [row0, row0 + rows), reads its A rows
+// through grp.row_src and the expert's matrix w + expert * N * K.
+template <typename E, bool GROUPED, int ACT>
+__global__ void __launch_bounds__(256) linear_tile_kernel(const E *__restrict__ w, int64_t N, int64_t K, const E *__restrict__ a,
+                                                          int64_t lda, int64_t T, float *__restrict__ c, E *__restrict__ c_act,
+                                                          int64_t ldc, ggb_moe_groups grp) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float sa[BK][BM + 4], sb[BK][BN + 4];
+    int64_t m0 = (int64_t)blockIdx.y * BM, m_end = T;
+    if (GROUPED) {
+        if ((int)blockIdx.y >= *grp.n_tiles) return;
+        const int e = grp.tile_expert[blockIdx.y];
+        m0 = grp.tile_row0[blockIdx.y];
+        m_end = grp.offsets[e + 1];
+        w += (int64_t)e * N * K;
+    }
+    const int64_t n0 = (int64_t)blockIdx.x * BN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    // loader: thread -> (row r = tid / 4, k quad (tid % 4) * 4) of both tiles
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    const int64_t am = m0 + lr;
+    const E *arow = nullptr;
+    if (am < m_end) arow = a + (GROUPED && grp.row_src ? (int64_t)grp.row_src[am] : am) * lda;
+    const E *wrow = n0 + lr < N ? w + (n0 + lr) * K : nullptr;
+    for (int64_t k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int64_t k = k0 + lk + u;
+            sa[lk + u][lr] = (arow && k < K) ? to_f32(arow[k]) : 0.f;
+            sb[lk + u][lr] = (wrow && k < K) ? to_f32(wrow[k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            const float4 av = *reinterpret_cast<const float4 *>(&sa[kk][ty * 4]);
+            const float4 bv = *reinterpret_cast<const float4 *>(&sb[kk][tx * 4]);
+            const float ar[4] = {av.x, av.y, av.z, av.w}, br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int64_t m = m0 + ty * 4 + i;
+        if (m >= m_end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int64_t n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (ACT == 1) { // square of relu, stored in the matrices' type (the next product's operand)
+                v = v > 0.f ? v * v : 0.f;
+                c_act[m * ldc + n] = from_f32<E>(v);
+            } else {
+                c[m * ldc + n] = v;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ norms
+// y = x / sqrt(mean(x^2) + eps) * w for up to two weights of the SAME x (a layer with two parallel branches norms
+// one x twice: the root mean square is computed once).  w_stride 0: the weight is one number; 1: a vector.
+template <typename E>
+__global__ void __launch_bounds__(256) rms_norm2_kernel(const float *__restrict__ x, int64_t ldx, const float *__restrict__ w1,
+                                                        int s1, const float *__restrict__ w2, int s2, float eps, int64_t n,
+                                                        E *__restrict__ y1, E *__restrict__ y2) {
+    __shared__ float red[8];
+    const float *xr = x + (int64_t)blockIdx.x * ldx;
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = warp_sum_f32(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)n + eps);
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = xr[i] * r;
+        if (y1) y1[(int64_t)blockIdx.x * n + i] = from_f32<E>(v * w1[s1 ? i : 0]);
+        if (y2) y2[(int64_t)blockIdx.x * n + i] = from_f32<E>(v * w2[s2 ? i : 0]);
+    }
+}
+
+// rows of x picked by index (the positions whose logits are wanted)
+__global__ void gather_rows_kernel(const float *__restrict__ x, const int32_t *__restrict__ rows, int64_t n, float *__restrict__ y) {
+    const float *src = x + (int64_t)rows[blockIdx.x] * n;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[(int64_t)blockIdx.x * n + i] = src[i];
+}
+
+template <typename E>
+__global__ void embed_rows_kernel(const E *__restrict__ table, const int32_t *__restrict__ ids, int64_t n, float *__restrict__ y) {
+    const E *src = table + (int64_t)ids[blockIdx.x] * n;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[(int64_t)blockIdx.x * n + i] = to_f32(src[i]);
+}
+
+// g = min(gate, limit), u = clamp(up, -limit, limit); y = g * sigmoid(alpha * g) * (u + 1).  gu rows hold the gate
+// half then the up half (one product with the two matrices stacked).
+template <typename E>
+__global__ void glu_clamp_kernel(const float *__restrict__ gu, int64_t F, int64_t T, float limit, float alpha, E *__restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * F) return;
+    const int64_t t = i / F, f = i - t * F;
+    const float g = fminf(gu[t * 2 * F + f], limit);
+    const float u = fminf(fmaxf(gu[t * 2 * F + F + f], -limit), limit);
+    y[i] = from_f32<E>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+
+// x <- x + a (+ f); then, with a side input, x <- x + rms(y) * nw, y = proj (gelu_tanh(gate x) * e), e = the token's
+// slice [e_off, e_off + sd) of its side-embedding row.  One CTA per token; x is staged in shared memory (fp32).
+template <typename E>
+__global__ void __launch_bounds__(256) residual_side_kernel(float *__restrict__ x, const float *__restrict__ a, const float *__restrict__ f,
+                                                            int64_t W, const int32_t *__restrict__ ids, const E *__restrict__ side_embed,
+                                                            int64_t e_ld, int64_t e_off, int sd, const E *__restrict__ w_gate,
+                                                            const E *__restrict__ w_proj, const float *__restrict__ nw, float eps) {
+    extern __shared__ float rs_smem[];
+    float *xs = rs_smem, *ys = xs + W, *gs = ys + W;
+    __shared__ float red[8];
+    const int64_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *xr = x + t * W;
+    for (int64_t i = tid; i < W; i += blockDim.x) {
+        float v = xr[i] + (f ? a[t * W + i] + f[t * W + i] : a[t * W + i]);
+        xs[i] = v;
+        if (!sd) xr[i] = v;
+    }
+    if (!sd) return;
+    __syncthreads();
+    const E *e = side_embed + (int64_t)ids[t] * e_ld + e_off;
+    for (int i = warp; i < sd; i += 8) {
+        float s = 0.f;
+        for (int64_t k = lane; k < W; k += 32) s = fmaf(to_f32(w_gate[(int64_t)i * W + k]), xs[k], s);
+        s = warp_sum_f32(s);
+        if (lane == 0) gs[i] = gelu_tanh_f32(s) * to_f32(e[i]);
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int64_t i = tid; i < W; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < sd; k++) s = fmaf(to_f32(w_proj[i * sd + k]), gs[k], s);
+        ys[i] = s;
+        ss = fmaf(s, s, ss);
+    }
+    ss = warp_sum_f32(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    const float r = 1.0f / sqrtf(tot / (float)W + eps);
+    for (int64_t i = tid; i < W; i += blockDim.x) xr[i] = xs[i] + ys[i] * r * nw[i];
+}
+
+template <typename E>
+__global__ void cvt_to_f32_kernel(const E *__restrict__ x, int64_t n, float *__restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = to_f32(x[i]);
+}
+
+template <typename E>
+int linear_launch(const E *w, int64_t N, int64_t K, const E *a, int64_t lda, int64_t T, float *c, int64_t ldc) {
+    cudaStream_t st = ggb_cuda_stream();
+    if (T <= kVecT) {
+        const dim3 grid((unsigned)((N + 7) / 8));
+        switch ((int)T) {
+#define VEC_CASE(TT) case TT: linear_vec_kernel<E, TT><<<grid, 256, 0, st>>>(w, N, K, a, lda, c, ldc); break;
+            VEC_CASE(1) VEC_CASE(2) VEC_CASE(3) VEC_CASE(4) VEC_CASE(5) VEC_CASE(6) VEC_CASE(7) VEC_CASE(8)
+#undef VEC_CASE
+        }
+    } else {
+        const dim3 grid((unsigned)((N + 63) / 64), (unsigned)((T + 63) / 64));
+        linear_tile_kernel<E, false, 0><<<grid, 256, 0, st>>>(w, N, K, a, lda, T, c, nullptr, ldc, ggb_moe_groups{});
+    }
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // namespace
+
+// the grouped form, for moe.cu
+int ggb_linear_grouped_launch(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int max_tiles, float *c,
+                              void *c_act, int64_t ldc, int act, const ggb_moe_groups &grp) {
+    cudaStream_t st = ggb_cuda_stream();
+    const dim3 grid((unsigned)((N + 63) / 64), (unsigned)max_tiles);
+#define GRP_CASE(E)                                                                                                           \
+    if (act) linear_tile_kernel<E, true, 1><<<grid, 256, 0, st>>>((const E *)w, N, K, (const E *)a, lda, 0, nullptr, (E *)c_act, ldc, grp); \
+    else linear_tile_kernel<E, true, 0><<<grid, 256, 0, st>>>((const E *)w, N, K, (const E *)a, lda, 0, c, nullptr, ldc, grp);
+    if (dt == GGB_TYPE_BF16) { GRP_CASE(__nv_bfloat16) } else { GRP_CASE(float) }
+#undef GRP_CASE
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+extern "C" {
+
+size_t ggb_dtype_size(int dt) { return dt == GGB_TYPE_BF16 ? 2 : dt == GGB_TYPE_F32 ? 4 : 0; }
+
+#define GGB_CHECK_DT(dt) GGB_CHECK_ARG((dt) == GGB_TYPE_BF16 || (dt) == GGB_TYPE_F32, "dtype %d is neither bf16 nor f32", (int)(dt))
+
+int ggb_op_linear(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int64_t T, float *c, int64_t ldc) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(w && a && c && N > 0 && K > 0 && T > 0 && lda >= K && ldc >= N, "linear: bad shape N=%lld K=%lld T=%lld",
+                  (long long)N, (long long)K, (long long)T);
+    if (dt == GGB_TYPE_BF16) {
+        if (ggb_gemm_dense_bf16_fits(N, K, T, ldc) && lda == K)
+            return ggb_gemm_dense_bf16(w, N, K, a, T, c, ldc);
+        return linear_launch((const __nv_bfloat16 *)w, N, K, (const __nv_bfloat16 *)a, lda, T, c, ldc);
+    }
+    return linear_launch((const float *)w, N, K, (const float *)a, lda, T, c, ldc);
+}
+
+int ggb_op_rms_norm2(int dt, const float *x, int64_t ldx, const float *w1, int w1_stride, const float *w2, int w2_stride, float eps,
+                     int64_t E, int64_t T, void *y1, void *y2) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(x && E > 0 && T > 0 && ldx >= E && (!y1 || w1) && (!y2 || w2), "rms_norm2: bad arguments");
+    if (dt == GGB_TYPE_BF16)
+        rms_norm2_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(x, ldx, w1, w1_stride, w2, w2_stride, eps, E, (__nv_bfloat16 *)y1,
+                                                                     (__nv_bfloat16 *)y2);
+    else
+        rms_norm2_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(x, ldx, w1, w1_stride, w2, w2_stride, eps, E, (float *)y1, (float *)y2);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_gather_rows_f32(const float *x, const int32_t *rows, int64_t n_rows, int64_t E, float *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(x && rows && y && n_rows > 0 && E > 0, "gather_rows: bad arguments");
+    gather_rows_kernel<<<(unsigned)n_rows, 256, 0, ggb_cuda_stream()>>>(x, rows, E, y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_embed_rows(int dt, const void *table, const int32_t *ids, int64_t T, int64_t E, float *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(table && ids && y && T > 0 && E > 0, "embed_rows: bad arguments");
+    if (dt == GGB_TYPE_BF16) embed_rows_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)table, ids, E, y);
+    else embed_rows_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const float *)table, ids, E, y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_glu_clamp(int dt, const float *gu, int64_t F, int64_t T, float limit, float alpha, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(gu && y && F > 0 && T > 0, "glu_clamp: bad arguments");
+    const unsigned blocks = (unsigned)((T * F + 255) / 256);
+    if (dt == GGB_TYPE_BF16) glu_clamp_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(gu, F, T, limit, alpha, (__nv_bfloat16 *)y);
+    else glu_clamp_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(gu, F, T, limit, alpha, (float *)y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_residual_side(int dt, float *x, const float *a, const float *f, int64_t W, int64_t T, const int32_t *ids, const void *side_embed,
+                         int64_t e_ld, int64_t e_off, int sd, const void *w_gate, const void *w_proj, const float *nw, float eps) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(x && a && W > 0 && T > 0 && sd >= 0, "residual_side: bad arguments");
+    GGB_CHECK_ARG(!sd || (ids && side_embed && w_gate && w_proj && nw), "residual_side: a side input needs its tensors");
+    const size_t smem = (size_t)(2 * W + sd) * sizeof(float);
+    GGB_CHECK_ARG(smem <= 200 * 1024, "residual_side: width %lld does not fit shared memory", (long long)W);
+    if (dt == GGB_TYPE_BF16) {
+        auto k = residual_side_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(x, a, f, W, ids, (const __nv_bfloat16 *)side_embed, e_ld, e_off, sd,
+                                                        (const __nv_bfloat16 *)w_gate, (const __nv_bfloat16 *)w_proj, nw, eps);
+    } else {
+        auto k = residual_side_kernel<float>;
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(x, a, f, W, ids, (const float *)side_embed, e_ld, e_off, sd, (const float *)w_gate,
+                                                        (const float *)w_proj, nw, eps);
+    }
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_cvt_bf16_f32(const void *x_bf16, int64_t n, float *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(x_bf16 && y && n > 0, "cvt_bf16_f32: bad arguments");
+    cvt_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)x_bf16, n, y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

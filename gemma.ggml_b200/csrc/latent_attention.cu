@@ -1,0 +1,350 @@
+// latent_attention.cu — attention over a compressed (latent) key/value cache.
+//
+// A caching layer stores per position ONE row [c | kr]: the normed latent c (R numbers) and the rotated key part kr
+// (Dr numbers) that all heads share.  A head's key is [W_uk_h c | kr] and its value W_uv_h c, so with
+//     qa_h = [W_uk_h^T q_h(unrotated) | rot(q_h(rotated))] * scale          (ggb_op_latent_q_absorb)
+// the score of head h against position j is qa_h . row_j, and the output is W_uv_h (sum_j p_j c_j)
+// (ggb_op_latent_attn_out): keys and values are never materialised, every head reads the same cache rows, and a layer
+// that borrows another layer's cache only brings its own W_uk / W_uv.  The soft-max carries a per-head sink: one more
+// term exp(sink_h) in the denominator that has no key and no value.
+//
+// Scores, soft-max and the weighted sums are fp32 whatever the storage type of the cache; -fmad=false: fmaf() spelled.
+// The cache is paged: position j lives in row table[j / B] * B + j % B.  Positions of a step's tokens are
+// *pos0 + t with *pos0 read on the device, so a captured step can be replayed at another position.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "dense.cuh"
+
+namespace {
+
+__device__ __forceinline__ int64_t cache_row(const int32_t *table, int B, int64_t j) { return (int64_t)table[j / B] * B + j % B; }
+
+// ---- c = rms(d[:R]) * nw, kr = rot(d[R:]) into the cache rows of the step's tokens.  One CTA per token.
+// cs: [n_pos][dims / 2][2] (cos, sin) with the rotation's magnitude factor already applied.
+template <typename E>
+__global__ void __launch_bounds__(128) latent_kv_store_kernel(const float *__restrict__ d, int64_t ldd, int R, int Dr, int dims,
+                                                              const float *__restrict__ nw, float eps, const float *__restrict__ cs,
+                                                              const int32_t *__restrict__ pos0, const int32_t *__restrict__ table,
+                                                              int B, E *__restrict__ cache, int64_t ldk) {
+    __shared__ float red[4];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float *dr = d + (int64_t)t * ldd;
+    const int64_t p = (int64_t)*pos0 + t;
+    E *row = cache + cache_row(table, B, p) * ldk;
+    float ss = 0.f;
+    for (int i = tid; i < R; i += 128) ss = fmaf(dr[i], dr[i], ss);
+    ss = warp_sum_f32(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float r = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)R + eps);
+    for (int i = tid; i < R; i += 128) row[i] = from_f32<E>(dr[i] * r * nw[i]);
+    const float *tab = cs + p * dims; // dims / 2 pairs of (cos, sin)
+    for (int i = tid; i < Dr / 2 + (Dr & 1); i += 128) {
+        const int i0 = 2 * i, i1 = 2 * i + 1;
+        if (i1 < dims) {
+            const float u = dr[R + i0], v = dr[R + i1], c = tab[2 * i], s = tab[2 * i + 1];
+            row[R + i0] = from_f32<E>(u * c - v * s);
+            row[R + i1] = from_f32<E>(v * c + u * s);
+        } else {
+            row[R + i0] = from_f32<E>(dr[R + i0]);
+            if (i1 < Dr) row[R + i1] = from_f32<E>(dr[R + i1]);
+        }
+    }
+}
+
+// ---- qa[t][h] = [W_uk_h^T qn | rot(qr)] * scale.  q rows hold, head by head, D unrotated then Dr rotated numbers.
+// A CTA takes kAbsT tokens of one head so that the head's W_uk slice is read once for all of them.
+constexpr int kAbsT = 8;
+template <typename E>
+__global__ void __launch_bounds__(256) latent_q_absorb_kernel(const float *__restrict__ q, int64_t ldq, int64_t T, int H, int D, int Dr,
+                                                              int dims, const float *__restrict__ cs, const int32_t *__restrict__ pos0,
+                                                              const E *__restrict__ w_uk, int R, float scale, float *__restrict__ qa) {
+    extern __shared__ float qs[]; // [kAbsT][D]
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const int64_t t0 = (int64_t)blockIdx.x * kAbsT;
+    const int nt = (int)min((int64_t)kAbsT, T - t0);
+    for (int i = tid; i < kAbsT * D; i += 256) {
+        const int tt = i / D, dd = i - tt * D;
+        qs[i] = tt < nt ? q[(t0 + tt) * ldq + (int64_t)h * (D + Dr) + dd] : 0.f;
+    }
+    __syncthreads();
+    const int QK = R + Dr;
+    for (int r = tid; r < R; r += 256) {
+        float acc[kAbsT];
+#pragma unroll
+        for (int tt = 0; tt < kAbsT; tt++) acc[tt] = 0.f;
+        const E *wc = w_uk + (int64_t)h * D * R + r;
+        for (int dd = 0; dd < D; dd++) {
+            const float w = to_f32(wc[(int64_t)dd * R]);
+#pragma unroll
+            for (int tt = 0; tt < kAbsT; tt++) acc[tt] = fmaf(qs[tt * D + dd], w, acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < kAbsT; tt++)
+            if (tt < nt) qa[((t0 + tt) * H + h) * QK + r] = acc[tt] * scale;
+    }
+    const int half = Dr / 2 + (Dr & 1);
+    for (int i = tid; i < nt * half; i += 256) {
+        const int tt = i / half, pi = i - tt * half;
+        const int64_t t = t0 + tt, p = (int64_t)*pos0 + t;
+        const float *src = q + t * ldq + (int64_t)h * (D + Dr) + D;
+        float *dst = qa + (t * H + h) * QK + R;
+        const int i0 = 2 * pi, i1 = i0 + 1;
+        if (i1 < dims) {
+            const float u = src[i0], v = src[i1], c = cs[p * dims + 2 * pi], s = cs[p * dims + 2 * pi + 1];
+            dst[i0] = (u * c - v * s) * scale;
+            dst[i1] = (v * c + u * s) * scale;
+        } else {
+            dst[i0] = src[i0] * scale;
+            if (i1 < Dr) dst[i1] = src[i1] * scale;
+        }
+    }
+}
+
+// ---- partial attention of one token over one split of its visible positions, all heads.
+// A tile of 32 cache rows is staged in shared memory once per group of NW heads (one warp per head): lane j scores
+// row j against the head's qa (shared memory, broadcast reads), the warp updates the running maximum / sum, and every
+// lane accumulates its R / 32 coordinates of sum_j p_j c_j.  part[t][split][h] = {m, l, acc[R]}.
+template <typename E> struct TileWord;
+template <> struct TileWord<float> {
+    static constexpr int per = 1;
+    static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) { return fmaf(__uint_as_float(w), q[0], acc); }
+};
+template <> struct TileWord<__nv_bfloat16> {
+    static constexpr int per = 2;
+    static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) {
+        acc = fmaf(__uint_as_float(w << 16), q[0], acc);
+        return fmaf(__uint_as_float(w & 0xffff0000u), q[1], acc);
+    }
+};
+
+template <typename E, int RC>
+__global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *__restrict__ qa, const E *__restrict__ cache, int64_t ldk,
+                                                                  const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
+                                                                  int H, int R, int Dr, int n_split, int SW, float *__restrict__ part) {
+    extern __shared__ uint32_t la_smem[];
+    constexpr int PER = TileWord<E>::per;
+    const int QK = R + Dr, words = (QK + PER - 1) / PER, QKp = words * PER;
+    uint32_t *tile = la_smem;                                     // [32][SW]
+    float *qsm = reinterpret_cast<float *>(la_smem + 32 * SW);    // [NW][QKp]
+    const int NW = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, split = blockIdx.y;
+    const int64_t n_kv = (int64_t)*pos0 + t + 1; // causal: the token sees itself and everything before
+    int64_t chunk = (n_kv + n_split - 1) / n_split;
+    chunk = (chunk + 31) / 32 * 32;
+    const int64_t j0 = (int64_t)split * chunk, j1 = min(j0 + chunk, n_kv);
+    for (int h0 = 0; h0 < H; h0 += NW) {
+        const int h = h0 + warp;
+        const bool live = h < H;
+        __syncthreads(); // the previous group's q and tile are no longer read
+        for (int i = threadIdx.x; i < NW * QKp; i += blockDim.x) {
+            const int w = i / QKp, k = i - w * QKp;
+            qsm[i] = (h0 + w < H && k < QK) ? qa[((int64_t)t * H + h0 + w) * QK + k] : 0.f;
+        }
+        float m = -INFINITY, l = 0.f, acc[RC];
+#pragma unroll
+        for (int i = 0; i < RC; i++) acc[i] = 0.f;
+        const float *qh = qsm + warp * QKp;
+        for (int64_t j = j0; j < j1; j += 32) {
+            __syncthreads();
+            const int rows = (int)min((int64_t)32, j1 - j);
+            for (int i = threadIdx.x; i < rows * words; i += blockDim.x) {
+                const int jj = i / words, w = i - jj * words;
+                tile[jj * SW + w] = reinterpret_cast<const uint32_t *>(cache + cache_row(table, B, j + jj) * ldk)[w];
+            }
+            __syncthreads();
+            if (!live) continue;
+            float s = -INFINITY;
+            if (lane < rows) {
+                const uint32_t *tr = tile + lane * SW;
+                float a0 = 0.f, a1 = 0.f;
+                int w = 0;
+                for (; w + 1 < words; w += 2) {
+                    a0 = TileWord<E>::dot(tr[w], qh + w * PER, a0);
+                    a1 = TileWord<E>::dot(tr[w + 1], qh + (w + 1) * PER, a1);
+                }
+                if (w < words) a0 = TileWord<E>::dot(tr[w], qh + w * PER, a0);
+                s = a0 + a1;
+            }
+            const float m_new = fmaxf(m, warp_max_f32(s));
+            const float corr = expf(m - m_new), p = expf(s - m_new); // exp(-inf) = 0: first tile, rows past the end
+            l = fmaf(l, corr, warp_sum_f32(p));
+            m = m_new;
+#pragma unroll
+            for (int i = 0; i < RC; i++) acc[i] *= corr;
+            for (int jj = 0; jj < rows; jj++) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const E *cr = reinterpret_cast<const E *>(tile + jj * SW);
+#pragma unroll
+                for (int i = 0; i < RC; i++)
+                    if (lane + 32 * i < R) acc[i] = fmaf(pj, to_f32(cr[lane + 32 * i]), acc[i]);
+            }
+        }
+        if (live) {
+            float *o = part + (((int64_t)t * n_split + split) * H + h) * (R + 2);
+            if (lane == 0) {
+                o[0] = m;
+                o[1] = l;
+            }
+#pragma unroll
+            for (int i = 0; i < RC; i++)
+                if (lane + 32 * i < R) o[2 + lane + 32 * i] = acc[i];
+        }
+    }
+}
+
+// ---- merge the splits with the sink, then out[t][h] = W_uv_h (sum_j p_j c_j).  kOutT tokens of one head per CTA.
+constexpr int kOutT = 8;
+template <typename E>
+__global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__restrict__ part, int n_split, const float *__restrict__ sink,
+                                                              const E *__restrict__ w_uv, int64_t T, int H, int R, int Dv,
+                                                              E *__restrict__ out) {
+    extern __shared__ float ol[]; // [kOutT][R]
+    const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t t0 = (int64_t)blockIdx.x * kOutT;
+    const int nt = (int)min((int64_t)kOutT, T - t0);
+    const float sk = sink[h];
+    for (int tt = 0; tt < kOutT; tt++) {
+        if (tt >= nt) {
+            for (int r = tid; r < R; r += 256) ol[tt * R + r] = 0.f;
+            continue;
+        }
+        const float *p0 = part + (((t0 + tt) * n_split) * H + h) * (R + 2);
+        const int64_t ps = (int64_t)H * (R + 2);
+        float M = sk;
+        for (int s = 0; s < n_split; s++) M = fmaxf(M, p0[s * ps]);
+        float L = expf(sk - M);
+        for (int s = 0; s < n_split; s++) L = fmaf(p0[s * ps + 1], expf(p0[s * ps] - M), L);
+        const float inv = 1.0f / L;
+        for (int r = tid; r < R; r += 256) {
+            float a = 0.f;
+            for (int s = 0; s < n_split; s++) a = fmaf(p0[s * ps + 2 + r], expf(p0[s * ps] - M), a);
+            ol[tt * R + r] = a * inv;
+        }
+    }
+    __syncthreads();
+    for (int v = warp; v < Dv; v += 8) {
+        const E *wr = w_uv + ((int64_t)h * Dv + v) * R;
+        float acc[kOutT];
+#pragma unroll
+        for (int tt = 0; tt < kOutT; tt++) acc[tt] = 0.f;
+        for (int k = lane; k < R; k += 32) {
+            const float w = to_f32(wr[k]);
+#pragma unroll
+            for (int tt = 0; tt < kOutT; tt++) acc[tt] = fmaf(w, ol[tt * R + k], acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < kOutT; tt++) {
+            const float s = warp_sum_f32(acc[tt]);
+            if (lane == 0 && tt < nt) out[(t0 + tt) * ((int64_t)H * Dv) + (int64_t)h * Dv + v] = from_f32<E>(s);
+        }
+    }
+}
+
+template <typename E>
+int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const int32_t *table, int B, const int32_t *pos0, int64_t T, int H,
+                        int R, int Dr, int n_split, float *part) {
+    constexpr int PER = TileWord<E>::per;
+    const int words = (R + Dr + PER - 1) / PER, SW = words | 1; // odd row pitch: lanes of a warp hit 32 different banks
+    const int NW = H < 16 ? H : 16;
+    const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * words * PER * 4;
+    GGB_CHECK_ARG(smem <= 200 * 1024, "latent_attn: rows of %d numbers do not fit shared memory", R + Dr);
+    const dim3 grid((unsigned)T, (unsigned)n_split);
+#define LA_CASE(RC)                                                                                                          \
+    {                                                                                                                        \
+        auto k = latent_attn_partial_kernel<E, RC>;                                                                          \
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, H, R, Dr, n_split, SW, part); \
+    }
+    if (R <= 64) LA_CASE(2)
+    else if (R <= 128) LA_CASE(4)
+    else if (R <= 256) LA_CASE(8)
+    else if (R <= 512) LA_CASE(16)
+    else LA_CASE(32)
+#undef LA_CASE
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+#define GGB_CHECK_DT(dt) GGB_CHECK_ARG((dt) == GGB_TYPE_BF16 || (dt) == GGB_TYPE_F32, "dtype %d is neither bf16 nor f32", (int)(dt))
+
+int64_t ggb_latent_cache_ld(int R, int Dr) { return ((int64_t)R + Dr + 7) / 8 * 8; }
+
+int ggb_op_latent_kv_store(int dt, const float *d, int64_t ldd, int64_t T, int R, int Dr, int rot_dims, const float *norm_w, float eps,
+                           const float *cos_sin, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(d && norm_w && cos_sin && pos0 && block_table && cache && T > 0 && R > 0 && Dr >= 0 && block_size > 0 &&
+                      rot_dims >= 0 && rot_dims <= Dr && rot_dims % 2 == 0,
+                  "latent_kv_store: bad arguments");
+    const int64_t ldk = ggb_latent_cache_ld(R, Dr);
+    if (dt == GGB_TYPE_BF16)
+        latent_kv_store_kernel<<<(unsigned)T, 128, 0, ggb_cuda_stream()>>>(d, ldd, R, Dr, rot_dims, norm_w, eps, cos_sin, pos0, block_table,
+                                                                           block_size, (__nv_bfloat16 *)cache, ldk);
+    else
+        latent_kv_store_kernel<<<(unsigned)T, 128, 0, ggb_cuda_stream()>>>(d, ldd, R, Dr, rot_dims, norm_w, eps, cos_sin, pos0, block_table,
+                                                                           block_size, (float *)cache, ldk);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_latent_q_absorb(int dt, const float *q, int64_t ldq, int64_t T, int H, int D, int Dr, int rot_dims, const float *cos_sin,
+                           const int32_t *pos0, const void *w_uk, int R, float scale, float *qa) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(q && cos_sin && pos0 && w_uk && qa && T > 0 && H > 0 && D > 0 && R > 0 && rot_dims <= Dr && rot_dims % 2 == 0,
+                  "latent_q_absorb: bad arguments");
+    const dim3 grid((unsigned)((T + kAbsT - 1) / kAbsT), (unsigned)H);
+    const size_t smem = (size_t)kAbsT * D * 4;
+    GGB_CHECK_ARG(smem <= 48 * 1024, "latent_q_absorb: head dimension %d too large", D);
+    if (dt == GGB_TYPE_BF16)
+        latent_q_absorb_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(q, ldq, T, H, D, Dr, rot_dims, cos_sin, pos0,
+                                                                       (const __nv_bfloat16 *)w_uk, R, scale, qa);
+    else
+        latent_q_absorb_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(q, ldq, T, H, D, Dr, rot_dims, cos_sin, pos0, (const float *)w_uk, R,
+                                                                       scale, qa);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+size_t ggb_latent_attn_scratch_bytes(int64_t T, int H, int R, int n_split) {
+    return (size_t)T * (size_t)n_split * (size_t)H * (size_t)(R + 2) * sizeof(float);
+}
+
+int ggb_op_latent_attn(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
+                       int64_t T, int H, int R, int Dr, int n_split, float *part) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(qa && cache && block_table && pos0 && part && T > 0 && H > 0 && R > 0 && R <= 1024 && Dr >= 0 && n_split > 0 &&
+                      n_split <= 65535 && block_size > 0,
+                  "latent_attn: bad arguments (latent size up to 1024)");
+    const int64_t ldk = ggb_latent_cache_ld(R, Dr);
+    if (dt == GGB_TYPE_BF16)
+        return attn_partial_launch<__nv_bfloat16>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, part);
+    return attn_partial_launch<float>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, part);
+}
+
+int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
+                           void *out) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(part && sink && w_uv && out && T > 0 && H > 0 && R > 0 && Dv > 0 && n_split > 0, "latent_attn_out: bad arguments");
+    const dim3 grid((unsigned)((T + kOutT - 1) / kOutT), (unsigned)H);
+    const size_t smem = (size_t)kOutT * R * 4;
+    GGB_CHECK_ARG(smem <= 48 * 1024, "latent_attn_out: latent size %d too large", R);
+    if (dt == GGB_TYPE_BF16)
+        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const __nv_bfloat16 *)w_uv, T, H, R, Dv,
+                                                                       (__nv_bfloat16 *)out);
+    else
+        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const float *)w_uv, T, H, R, Dv, (float *)out);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

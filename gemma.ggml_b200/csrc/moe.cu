@@ -1,0 +1,171 @@
+// moe.cu — mixture of experts: the router (fp32 logits, the `top` largest, soft-max over the chosen ones only), the
+// grouping of (token, slot) pairs by expert, the two grouped products (dense.cu: linear_tile_kernel, GROUPED) and the
+// weighted sum.  A token's result does not depend on which other tokens share the step: every slot is computed by
+// itself in k order and the `top` slot outputs are added in slot order.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "dense.cuh"
+
+namespace {
+
+// one CTA (4 warps) per token: z[e] = w[e] . h + b[e]; then `top` rounds of arg-max (ties: the lower index)
+template <typename E>
+__global__ void __launch_bounds__(128) moe_route_kernel(const E *__restrict__ h, int64_t W, const float *__restrict__ w,
+                                                        const float *__restrict__ b, int n_exp, int top, int32_t *__restrict__ idx,
+                                                        float *__restrict__ wt) {
+    extern __shared__ float z[]; // [n_exp] logits, then [top] chosen values
+    float *sel = z + n_exp;
+    const int64_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const E *hr = h + t * W;
+    for (int e = warp; e < n_exp; e += 4) {
+        float s = 0.f;
+        for (int64_t k = lane; k < W; k += 32) s = fmaf(w[(int64_t)e * W + k], to_f32(hr[k]), s);
+        s = warp_sum_f32(s);
+        if (lane == 0) z[e] = s + (b ? b[e] : 0.f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    for (int k = 0; k < top; k++) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < n_exp; e += 32) {
+            const float v = z[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            idx[t * top + k] = bi;
+            sel[k] = bv;
+            z[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float m = sel[0], sum = 0.f; // sel[0] is the largest
+        for (int k = 0; k < top; k++) {
+            sel[k] = expf(sel[k] - m);
+            sum += sel[k];
+        }
+        for (int k = 0; k < top; k++) wt[t * top + k] = sel[k] / sum;
+    }
+}
+
+// one CTA: counts per expert, offsets, the list of 64-row tiles, and the sorted order of the n = T * top slots
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ idx, int n, int top, int n_exp, int32_t *offsets,
+                                                         int32_t *row_src, int32_t *inv, int32_t *tile_expert, int32_t *tile_row0,
+                                                         int32_t *n_tiles) {
+    extern __shared__ int32_t cnt[]; // [n_exp] counts, then cursors
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int s = threadIdx.x; s < n; s += blockDim.x) atomicAdd(&cnt[idx[s]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, nt = 0;
+        for (int e = 0; e < n_exp; e++) {
+            const int c = cnt[e];
+            offsets[e] = off;
+            cnt[e] = off;
+            for (int r = off; r < off + c; r += 64) {
+                tile_expert[nt] = e;
+                tile_row0[nt] = r;
+                nt++;
+            }
+            off += c;
+        }
+        offsets[n_exp] = off;
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int s = threadIdx.x; s < n; s += blockDim.x) {
+        const int p = atomicAdd(&cnt[idx[s]], 1);
+        row_src[p] = s / top;
+        inv[s] = p;
+    }
+}
+
+__global__ void moe_combine_kernel(const float *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ wt, int top,
+                                   int64_t W, float *__restrict__ out) {
+    const int64_t t = blockIdx.x;
+    for (int64_t i = threadIdx.x; i < W; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < top; k++) s = fmaf(wt[t * top + k], y[(int64_t)inv[t * top + k] * W + i], s);
+        out[t * W + i] = s;
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+#define GGB_CHECK_DT(dt) GGB_CHECK_ARG((dt) == GGB_TYPE_BF16 || (dt) == GGB_TYPE_F32, "dtype %d is neither bf16 nor f32", (int)(dt))
+
+int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *bias, int n_exp, int top,
+                     int32_t *idx, float *wt) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(h && w_router && idx && wt && W > 0 && T > 0 && n_exp > 0 && top > 0 && top <= n_exp && n_exp <= 8192,
+                  "moe_route: bad arguments");
+    const size_t smem = (size_t)(n_exp + top) * 4;
+    if (dt == GGB_TYPE_BF16)
+        moe_route_kernel<<<(unsigned)T, 128, smem, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, w_router, bias, n_exp, top, idx, wt);
+    else
+        moe_route_kernel<<<(unsigned)T, 128, smem, ggb_cuda_stream()>>>((const float *)h, W, w_router, bias, n_exp, top, idx, wt);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_moe_max_tiles(int64_t n_slots, int n_exp) { return (int)(n_slots / 64) + n_exp; }
+size_t ggb_moe_group_ints(int64_t n_slots, int n_exp) {
+    return (size_t)(n_exp + 1) + 2 * (size_t)n_slots + 2 * (size_t)ggb_moe_max_tiles(n_slots, n_exp) + 1;
+}
+
+static ggb_moe_groups groups_of(int32_t *ws, int64_t n, int n_exp, bool gather) {
+    ggb_moe_groups g;
+    const int mt = ggb_moe_max_tiles(n, n_exp);
+    g.offsets = ws;
+    g.row_src = gather ? ws + n_exp + 1 : nullptr;
+    g.tile_expert = ws + n_exp + 1 + 2 * n;
+    g.tile_row0 = g.tile_expert + mt;
+    g.n_tiles = g.tile_row0 + mt;
+    return g;
+}
+
+int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t *ws) {
+    GGB_REQUIRE_INIT();
+    const int64_t n = T * top;
+    GGB_CHECK_ARG(idx && ws && T > 0 && top > 0 && n_exp > 0 && n_exp <= 8192 && n < (1ll << 30), "moe_group: bad arguments");
+    const int mt = ggb_moe_max_tiles(n, n_exp);
+    int32_t *offsets = ws, *row_src = ws + n_exp + 1, *inv = row_src + n, *te = inv + n, *tr = te + mt, *nt = tr + mt;
+    moe_group_kernel<<<1, 1024, (size_t)n_exp * 4, ggb_cuda_stream()>>>(idx, (int)n, top, n_exp, offsets, row_src, inv, te, tr, nt);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int gather, int64_t T, int top, int n_exp,
+                      const int32_t *ws, int act, void *c, int64_t ldc) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(w && a && ws && c && N > 0 && K > 0 && T > 0 && lda >= K && ldc >= N, "moe_linear: bad arguments");
+    const ggb_moe_groups g = groups_of(const_cast<int32_t *>(ws), T * top, n_exp, gather != 0);
+    return ggb_linear_grouped_launch(dt, w, N, K, a, lda, ggb_moe_max_tiles(T * top, n_exp), act ? nullptr : (float *)c, act ? c : nullptr,
+                                     ldc, act, g);
+}
+
+int ggb_op_moe_combine(const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, float *out) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(y && ws && wt && out && T > 0 && top > 0 && W > 0, "moe_combine: bad arguments");
+    const int32_t *inv = ws + n_exp + 1 + T * top;
+    moe_combine_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(y, inv, wt, top, W, out);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

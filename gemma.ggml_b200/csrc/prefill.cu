@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "dense.cuh"
 
 namespace {
 
@@ -821,3 +822,7 @@ int ggb_op_attn_prefill(const float *q, const void *kcache, const void *vcache, 
 }
 
 } // extern "C"
+
+// the GEMM on plain bf16 matrices (both operands copied by cp.async, nothing to dequantise)
+bool ggb_gemm_dense_bf16_fits(int64_t N, int64_t K, int64_t T, int64_t ldc) { return false; }
+int ggb_gemm_dense_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t T, float *c, int64_t ldc) { return GGB_ERR_UNSUPPORTED; }

@@ -1,11 +1,14 @@
 // capi.cpp — flat C entry points over gemma_model so tests / bench.py can drive the host side with
 // ctypes (the reference drives its model from app::run, ref: src/app.cpp:30-44).
+#include <cstdio>
 #include <cstring>
 #include <string>
 #include <vector>
 
 #include "gemma_model.h"
 #include "gguf_loader.h"
+#include "lm_engine.h"
+#include "safolorn_model.h"
 #include "tensor_dump.h"
 
 extern "C" {
@@ -121,6 +124,88 @@ int gm_get_capture(void *m, const char *name, int layer, float *host, int64_t n)
 int gm_get_kv(void *m, int layer, void *k_host, void *v_host) { return ((gemma_model *)m)->get_kv(layer, k_host, v_host); }
 int gm_kernels_per_step(void *m) { return ((gemma_model *)m)->kernels_per_step(); }
 uint64_t gm_weight_bytes(void *m) { return (uint64_t)((gemma_model *)m)->weight_bytes(); }
+
+// ---- the serving engine over the architecture registry (host/lm_engine.h): a model folder with config.json and
+// model.safetensors (or a configuration text with random weights), sequences by name, steps of token portions
+void *lm_engine_open(const char *dir, const char *config_text, int dtype, int64_t max_tokens, int page_size, int max_seqs,
+                     int max_portion, int random_weights, uint64_t seed) {
+    lm_load_options opt;
+    opt.dtype = dtype;
+    opt.max_tokens = max_tokens;
+    opt.max_portion = max_portion;
+    opt.random_weights = random_weights != 0;
+    opt.seed = seed;
+    lm_model *m = config_text && *config_text ? lm_load_config(config_text, dir ? dir : "", opt, &g_capi_err)
+                                              : lm_load(dir ? dir : "", opt, &g_capi_err);
+    if (!m) return nullptr;
+    lm_engine *e = new lm_engine();
+    if (e->init(m, max_tokens, page_size, max_seqs)) {
+        g_capi_err = e->error();
+        delete e;
+        return nullptr;
+    }
+    return e;
+}
+void lm_engine_close(void *e) { delete (lm_engine *)e; }
+const char *lm_engine_error(void *e) { return ((lm_engine *)e)->error().c_str(); }
+int lm_engine_vocab(void *e) { return ((lm_engine *)e)->model()->vocab(); }
+const char *lm_engine_architecture(void *e) { return ((lm_engine *)e)->model()->architecture(); }
+// entries: ids[i], tokens[i][n_tokens[i]], want[i][n_want[i]]; logits_out receives sum(n_want) rows of vocab floats
+int lm_engine_step(void *e, int n_entries, const char *const *ids, const int32_t *const *tokens, const int32_t *n_tokens,
+                   const int32_t *const *want, const int32_t *n_want, int n_end, const char *const *end_ids, float *logits_out) {
+    std::vector<lm_entry> es((size_t)n_entries);
+    for (int i = 0; i < n_entries; i++) {
+        es[(size_t)i].id = ids[i];
+        es[(size_t)i].tokens.assign(tokens[i], tokens[i] + n_tokens[i]);
+        es[(size_t)i].want.assign(want[i], want[i] + n_want[i]);
+    }
+    std::vector<std::string> end;
+    for (int i = 0; i < n_end; i++) end.push_back(end_ids[i]);
+    std::vector<float> logits;
+    const int rc = ((lm_engine *)e)->step(es, end, &logits);
+    if (rc) return rc;
+    if (logits_out && !logits.empty()) memcpy(logits_out, logits.data(), logits.size() * 4);
+    return 0;
+}
+int lm_engine_generate(void *e, const char *id, const int32_t *prompt, int n_prompt, int n_new, int32_t *out) {
+    std::vector<int32_t> o;
+    const int rc = ((lm_engine *)e)->generate(id, std::vector<int32_t>(prompt, prompt + n_prompt), n_new, &o);
+    if (rc) return rc;
+    memcpy(out, o.data(), o.size() * 4);
+    return 0;
+}
+// out[6] = {live sequences, free pages, pages, page size, kernels of the last forward call, weight bytes}
+int lm_engine_stats(void *e, int64_t *out) {
+    lm_engine *g = (lm_engine *)e;
+    out[0] = g->live_seqs();
+    out[1] = g->cache()->free_pages();
+    out[2] = g->cache()->n_pages();
+    out[3] = g->cache()->page_size();
+    safolorn_model *sf = dynamic_cast<safolorn_model *>(g->model());
+    out[4] = sf ? sf->kernels_last_forward() : 0;
+    out[5] = sf ? (int64_t)sf->weight_bytes() : 0;
+    return 0;
+}
+int64_t lm_engine_seq_len(void *e, const char *id) { return ((lm_engine *)e)->seq_len(id); }
+// pages of a live sequence (host copy): returns their number, fills at most cap
+int lm_engine_seq_pages(void *e, const char *id, int32_t *out, int cap) { return ((lm_engine *)e)->seq_pages(id, out, cap); }
+int lm_engine_capture(void *e, int on) {
+    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
+    if (!sf) return -1;
+    sf->set_capture(on != 0);
+    return 0;
+}
+int lm_engine_get_capture(void *e, int layer, float *host, int64_t n) {
+    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
+    return sf ? sf->get_capture(layer, host, n) : -1;
+}
+// the registered architecture names, comma separated
+int lm_architectures_csv(char *buf, int cap) {
+    std::string s;
+    for (const auto &a : lm_architectures()) s += (s.empty() ? "" : ",") + a;
+    snprintf(buf, (size_t)cap, "%s", s.c_str());
+    return (int)s.size();
+}
 
 // ---- tensor_dump (ref: src/tensor_dump.h): host-side parity harness
 void td_set_dir(const char *dir) { set_tensor_dump_dir(dir); }

@@ -33,7 +33,7 @@ typedef enum {
 
 /* ggml_type values the path uses (upstream enum ids; ref: src/hpc.cpp:132-143) */
 enum { GGB_TYPE_F32 = 0, GGB_TYPE_F16 = 1, GGB_TYPE_Q4_0 = 2, GGB_TYPE_Q8_0 = 8,
-       GGB_TYPE_Q4_K = 12, GGB_TYPE_Q6_K = 14, GGB_TYPE_Q8_K = 15 }; /* ggml_type ids */
+       GGB_TYPE_Q4_K = 12, GGB_TYPE_Q6_K = 14, GGB_TYPE_Q8_K = 15, GGB_TYPE_BF16 = 30 }; /* ggml_type ids */
 
 /* Arithmetic: every result of the Q4_0 / Q8_0 decode path and of the K-quant operators is BIT-IDENTICAL to the scalar
  * ggml code the reference's CPU path runs (one fp32 accumulator per row, blocks in order; double accumulators where
@@ -248,6 +248,65 @@ int ggb_op_geglu_bf16(const float *gate, const float *up, int64_t n, void *y_bf1
 /* out (fp32) and / or out_bf16 (the o-projection's A operand, same rounding as ggb_op_cvt_f32_bf16) may be NULL */
 int ggb_op_attn_prefill(const float *q, const void *kcache, const void *vcache, int64_t T, int pos0, int H, int Hkv, int d,
                         float *out, void *out_bf16);
+
+/* ------------------------------------------------------------------ plain bf16 / fp32 matrices (csrc/dense.cu)
+ * Operators of models whose matrices are stored unquantised, row-major [out][in] and applied as W x.  `dt` is
+ * GGB_TYPE_BF16 (matrices and the activations that feed them are bf16, products accumulate in fp32) or GGB_TYPE_F32
+ * (true fp32 everywhere, no reduced-precision matrix mode).  The residual stream, norms, soft-max and every other
+ * reduction are fp32 in both.  Pointers typed void* are in `dt`. */
+size_t ggb_dtype_size(int dt);
+/* c[t][n] (fp32) = sum_k a[t][k] w[n][k]: a streaming mat-vec for T <= 8, the tcgen05 GEMM for aligned bf16 shapes
+ * (K %% 64 == 0, N %% 32 == 0, lda == K, T >= 64), a shared-memory tile kernel for every other shape */
+int ggb_op_linear(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int64_t T, float *c, int64_t ldc);
+/* y = x / sqrt(mean(x^2) + eps) * w for up to two weights of the same rows (the root mean square is computed once);
+ * w_stride 0: the weight is one number, 1: a vector of E; y1 / y2 ([T][E] in dt) may be NULL */
+int ggb_op_rms_norm2(int dt, const float *x, int64_t ldx, const float *w1, int w1_stride, const float *w2, int w2_stride, float eps,
+                     int64_t E, int64_t T, void *y1, void *y2);
+int ggb_op_gather_rows_f32(const float *x, const int32_t *rows, int64_t n_rows, int64_t E, float *y);
+int ggb_op_embed_rows(int dt, const void *table, const int32_t *ids, int64_t T, int64_t E, float *y);
+/* gu rows = [gate F | up F]: g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha g) * (u + 1) */
+int ggb_op_glu_clamp(int dt, const float *gu, int64_t F, int64_t T, float limit, float alpha, void *y);
+/* x <- x + a (+ f, may be NULL); with sd > 0 then the per-token side input: e = side_embed[ids[t]][e_off .. e_off + sd),
+ * y = w_proj (gelu_tanh(w_gate x) * e), x <- x + y / sqrt(mean(y^2) + eps) * nw */
+int ggb_op_residual_side(int dt, float *x, const float *a, const float *f, int64_t W, int64_t T, const int32_t *ids, const void *side_embed,
+                         int64_t e_ld, int64_t e_off, int sd, const void *w_gate, const void *w_proj, const float *nw, float eps);
+int ggb_op_cvt_bf16_f32(const void *x_bf16, int64_t n, float *y);
+
+/* ------------------------------------------------------------------ latent attention (csrc/latent_attention.cu)
+ * The cache of a layer holds one row [c (R) | kr (Dr)] per position, ggb_latent_cache_ld(R, Dr) numbers apart, in pages
+ * of block_size positions: position j is row block_table[j / block_size] * block_size + j %% block_size.  The step's
+ * tokens sit at positions *pos0 + t (pos0 and block_table are device int32: a captured step replays elsewhere).
+ * cos_sin: [positions][rot_dims / 2][2] fp32, pairs (2i, 2i+1) of the first rot_dims rotated numbers are turned. */
+int64_t ggb_latent_cache_ld(int R, int Dr);
+/* d rows = [R latent | Dr key part] (fp32, the down-projection's output): cache row <- [rms(d[:R]) * norm_w | rot(d[R:])] */
+int ggb_op_latent_kv_store(int dt, const float *d, int64_t ldd, int64_t T, int R, int Dr, int rot_dims, const float *norm_w, float eps,
+                           const float *cos_sin, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache);
+/* q rows hold per head D unrotated then Dr rotated numbers; qa[t][h] = [w_uk_h^T q_unrot | rot(q_rot)] * scale, R + Dr fp32 */
+int ggb_op_latent_q_absorb(int dt, const float *q, int64_t ldq, int64_t T, int H, int D, int Dr, int rot_dims, const float *cos_sin,
+                           const int32_t *pos0, const void *w_uk, int R, float scale, float *qa);
+/* causal soft-max attention of T tokens over the cache, the visible positions of a token cut into n_split parts:
+ * part[t][split][h] = {running max, sum, sum_j p_j c_j (R)} */
+size_t ggb_latent_attn_scratch_bytes(int64_t T, int H, int R, int n_split);
+int ggb_op_latent_attn(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
+                       int64_t T, int H, int R, int Dr, int n_split, float *part);
+/* merges the parts with the per-head sink (one more exp(sink_h) in the denominator, no value) and applies w_uv:
+ * out[t][h * Dv ..] (dt) = w_uv_h (sum_j p_j c_j) */
+int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
+                           void *out);
+
+/* ------------------------------------------------------------------ mixture of experts (csrc/moe.cu)
+ * route: fp32 logits w_router h + bias, the `top` largest (ties: lower index), weights = soft-max over the chosen.
+ * group: sorts the T * top slots by expert into `ws` (ggb_moe_group_ints int32).  moe_linear: per expert
+ * c[sorted row] = a[row] w_e^T with w = [n_exp][N][K]; gather: a is indexed by token (first product), else by sorted
+ * row; act 1: c = relu(.)^2 in dt, act 0: c fp32.  combine: out[t] = sum_s wt[t][s] y[sorted row of slot s]. */
+int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *bias, int n_exp, int top,
+                     int32_t *idx, float *wt);
+int ggb_moe_max_tiles(int64_t n_slots, int n_exp);
+size_t ggb_moe_group_ints(int64_t n_slots, int n_exp);
+int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t *ws);
+int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int gather, int64_t T, int top, int n_exp,
+                      const int32_t *ws, int act, void *c, int64_t ldc);
+int ggb_op_moe_combine(const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, float *out);
 
 /* ------------------------------------------------------------------ fused decode step
  * The whole per-token node list (ref: src/gemma_model.cpp:665-747) as ONE persistent cooperative
