@@ -181,6 +181,8 @@ _HOST_SIG = {
     "lm_engine_seq_pages": (i32, [vp, C.c_char_p, vp, i32]),
     "lm_engine_capture": (i32, [vp, i32]), "lm_engine_get_capture": (i32, [vp, i32, vp, i64]),
     "lm_architectures_csv": (i32, [C.c_char_p, i32]),
+    "sf_config_probe": (i32, [C.c_char_p, P(i64)]),
+    "st_probe": (i32, [C.c_char_p, C.c_char_p, P(i64), P(i64), C.c_char_p, i32, P(i64)]),
     "mul_mat": (None, [i64, i64, i64, i64, i64, i64, i64, sz, i64, vp, vp, vp, vp, i32, vp]),
     "init_cuda_offload": (i32, [i32]),
 }

@@ -199,6 +199,31 @@ int lm_engine_get_capture(void *e, int layer, float *host, int64_t n) {
     safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
     return sf ? sf->get_capture(layer, host, n) : -1;
 }
+// host only: parses a Safolorn configuration text; out[5] = {layers, caching layers, vocab, width, side dim}; -1 and
+// gm_last_error() when the configuration is refused
+int sf_config_probe(const char *text, int64_t *out) {
+    json_value j;
+    sf_config c;
+    if (!json_parser(text, strlen(text)).parse(&j, &g_capi_err)) return -1;
+    if (sf_parse_config(j, &c, &g_capi_err)) return -1;
+    int64_t own = 0;
+    for (const auto &l : c.layers) own += l.kv_from < 0;
+    out[0] = (int64_t)c.layers.size(); out[1] = own; out[2] = c.vocab; out[3] = c.width; out[4] = c.side_dim;
+    return 0;
+}
+// host only: a tensor of a .safetensors file: returns its number of dimensions (shape[0 .. 8) filled, *nbytes, dtype text),
+// -1 when the file cannot be read, -2 when the tensor is not there
+int st_probe(const char *path, const char *name, int64_t *shape, int64_t *nbytes, char *dtype, int dtype_cap, int64_t *n_tensors) {
+    safetensors_file f;
+    if (f.open(path, &g_capi_err)) return -1;
+    if (n_tensors) *n_tensors = (int64_t)f.tensors().size();
+    const st_tensor *t = f.find(name);
+    if (!t) return -2;
+    for (size_t i = 0; i < t->shape.size() && i < 8; i++) shape[i] = t->shape[i];
+    if (nbytes) *nbytes = (int64_t)t->nbytes;
+    if (dtype) snprintf(dtype, (size_t)dtype_cap, "%s", t->dtype.c_str());
+    return (int)t->shape.size();
+}
 // the registered architecture names, comma separated
 int lm_architectures_csv(char *buf, int cap) {
     std::string s;

@@ -308,8 +308,10 @@ int safolorn_model::load(const safetensors_file *file, uint64_t seed) {
             SF_TRY(upload_matrix(down, &w.e_down));
             SF_GET(p + "mlp.router", l.experts, W, 2.0f * aw, 0.f, &a);
             SF_TRY(upload_f32(a, &w.router));
-            SF_GET(p + "mlp.router.b", 1, l.experts, 0.5f, 0.f, &a);
-            SF_TRY(upload_f32(a, &w.router_b));
+            if (!file || file->find(p + "mlp.router.b")) { // a router without a bias adds none
+                SF_GET(p + "mlp.router.b", 1, l.experts, 0.5f, 0.f, &a);
+                SF_TRY(upload_f32(a, &w.router_b));
+            }
         }
         if (c.side_dim > 0) {
             SF_GET(p + "side.gate", c.side_dim, W, aw, 0.f, &a);
