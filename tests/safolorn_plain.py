@@ -18,7 +18,7 @@ def rms(x, eps):
 
 def norm_one_number(x, g, eps):
     """RMS norm whose weight is one number for all coordinates."""
-    return rms(x, eps) * float(g)
+    return rms(x, eps) * float(np.asarray(g).reshape(-1)[0])
 
 
 def norm_plain(x, w, eps):

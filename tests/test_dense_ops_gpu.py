@@ -12,8 +12,19 @@ pytestmark = pytest.mark.gpu
 BF16, F32 = 30, 0
 
 
+_ALIVE = []
+
+
+@pytest.fixture(autouse=True)
+def _release_buffers():
+    yield
+    _ALIVE.clear()
+
+
 def dev(G, a):
-    return G.DeviceBuffer.from_numpy(np.ascontiguousarray(a))
+    """an uploaded copy that stays allocated until the test ends (launches are asynchronous)"""
+    _ALIVE.append(G.DeviceBuffer.from_numpy(np.ascontiguousarray(a)))
+    return _ALIVE[-1]
 
 
 def as_dt(dt, a):
