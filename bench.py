@@ -570,8 +570,174 @@ def run_prefill(args):
     print(json.dumps(line), flush=True)
 
 
+SAFOLORN_SIZES = {
+    # width, layers, heads, dim, rot_dim, vdim, kv_rank, dense ff, experts, top, expert ff, vocab
+    "s": (1024, 8, 8, 64, 32, 64, 256, 4096, 16, 2, 1024, 32000),
+    "m": (2048, 8, 16, 128, 64, 128, 512, 8192, 32, 4, 1408, 32000),
+    "l": (4096, 4, 32, 128, 64, 128, 512, 12288, 16, 2, 2048, 32000),
+}
+
+
+def safolorn_config(size):
+    """Layers in the pattern own-cache/dense, own-cache/experts, borrowed-cache/dense, borrowed-cache/experts."""
+    W, L, H, D, Dr, Dv, R, ff, E, top, eff, V = SAFOLORN_SIZES[size]
+    rot = {"base": 10000.0, "dims": Dr, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    layers = []
+    for i in range(L):
+        mx = {"heads": H, "dim": D, "rot_dim": Dr, "vdim": Dv, "kv_rank": R, "scale": 1.0 / (D + Dr) ** 0.5, "rot": rot}
+        if i % 4 >= 2:
+            mx["kv_from"] = i - 2
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0} if i % 2 == 0 else \
+            {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}}
+        layers.append({"type": "latent_attention", "mixer": mx, "mlp": mlp})
+    return {"architecture": "Safolorn", "vocab": V, "width": W, "norm": {"eps": 1e-5}, "token_side": {"dim": 64}, "layers": layers}
+
+
+def run_safolorn(args):
+    """--arch safolorn: prefill and decode throughput of the Safolorn design (random bf16 weights) at layer sizes of real
+    models, through the serving engine (host call: H2D token ids, operator launches / graph replay, D2H result), with
+    cudaEvent time per operator class and roofline fractions of the matrix and attention operators; beside it the
+    Gemma path (Q8_0 weights) at the same width, depth, heads and feed-forward size."""
+    import gemma_ggml_b200 as G
+    G.init(0)
+    L = G.cuda_lib()
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks = {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops_sustained": float(pk["bf16_tflops_sustained"]), "source": "MEASURED_PEAKS.json"}
+    except Exception:
+        pass
+    T, ctx, n_dec = args.prefill_tokens if args.prefill_tokens != 512 else 2048, args.ctx, min(args.steps, 128)
+    records = {}
+    for size in args.sizes.split(","):
+        cfg = safolorn_config(size)
+        W, nl, H, D, Dr, Dv, R, ff, E, top, eff, V = SAFOLORN_SIZES[size]
+        eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+        r = np.random.default_rng(0)
+        prompt = r.integers(0, V, T).astype(np.int32)
+
+        def prefill():
+            eng.step([("p", prompt, [T - 1])], ["p"])
+        for _ in range(3):
+            prefill()
+        reps = 5
+        with ClockSampler(0) as clocks:
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                prefill()
+            pf = (time.perf_counter() - t0) / reps
+        L.ggb_prof_enable(1)
+        G.prof_reset()
+        prefill()
+        G.sync()
+        pf_ops = {k: G.prof_get(k)[0] for k in ("op_linear", "op_attn", "op_attn_prep", "op_attn_out", "op_moe", "op_moe_linear", "op_norm", "op_act", "op_residual", "op_rows")}
+        L.ggb_prof_enable(0)
+        # algorithmic work of one prefill
+        lin_flops = moe_flops = attn_flops = 0.0
+        lin_bytes = moe_bytes = 0.0
+        for i, Ly in enumerate(cfg["layers"]):
+            own = "kv_from" not in Ly["mixer"]
+            n_lin = H * (D + Dr) * W + (own and (R + Dr) * W or 0) + W * H * Dv
+            if Ly["mlp"]["kind"] == "dense":
+                n_lin += 3 * ff * W
+            else:
+                moe_flops += 2.0 * T * top * 2 * eff * W
+                moe_bytes += 2.0 * top * 2 * eff * W  # decode: the chosen experts only
+            lin_flops += 2.0 * T * n_lin
+            lin_bytes += 2.0 * n_lin
+            attn_flops += 2.0 * H * (2 * R + Dr) * T * (T + 1) / 2
+        lin_flops += 2.0 * V * W  # one row of logits
+        lin_bytes += 2.0 * V * W
+        # decode at n_kv ~ ctx: fill the cache with a prompt, then greedy tokens through the captured one-token step
+        eng.step([("d", r.integers(0, V, ctx - 1).astype(np.int32), [])])
+        eng.generate("d", [1], 8)
+        t0 = time.perf_counter()
+        eng.generate("d", [2], n_dec)
+        dec = (time.perf_counter() - t0) / n_dec
+        kernels = eng.stats()["kernels_last_forward"]
+        eng.use_graphs(False)
+        eng.generate("d", [3], 4)
+        L.ggb_prof_enable(1)
+        G.prof_reset()
+        eng.generate("d", [4], 8)
+        G.sync()
+        dc_ops = {k: G.prof_get(k)[0] / 8 for k in pf_ops}
+        L.ggb_prof_enable(0)
+        eng.end("d")
+        n_cache = sum("kv_from" not in Ly["mixer"] for Ly in cfg["layers"])
+        cache_bytes = 2.0 * nl * ctx * (R + Dr)  # every layer reads a cache (its own or a borrowed one)
+        wbytes = eng.stats()["weight_bytes"]
+        eng.close()
+        rec = {
+            "config": {"width": W, "layers": nl, "heads": H, "dim": D, "rot_dim": Dr, "vdim": Dv, "kv_rank": R, "ff": ff, "experts": E, "top": top,
+                       "expert_ff": eff, "vocab": V, "caching_layers": n_cache, "weight_bytes": wbytes},
+            "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks.summary(),
+                        "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
+                        "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                        "moe_linear_tflops": moe_flops / (pf_ops["op_moe_linear"] / 1e3) / 1e12,
+                        "attn_tflops_cuda_cores": attn_flops / (pf_ops["op_attn"] / 1e3) / 1e12},
+            "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
+                       "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                       "moe_linear_gbs": moe_bytes / (dc_ops["op_moe_linear"] / 1e3) / 1e9,
+                       "attn_gbs": cache_bytes / (dc_ops["op_attn"] / 1e3) / 1e9,
+                       "token_frac_of_hbm_roofline": ((lin_bytes + moe_bytes + cache_bytes) / (peaks["hbm_gbs"] * 1e9)) / dec},
+        }
+        # the closest existing model at equal size: the Gemma path, Q8_0, same width / depth / heads / feed-forward
+        if not args.no_sub_records:
+            dims = dict(n_embd=W, n_layer=nl, n_head=H, n_head_kv=H, head_dim=D + Dr if (D + Dr) % 64 == 0 else 128, n_ff=ff, n_vocab=V, n_ctx=ctx + 8)
+            m = G.GemmaModel(G.make_config(wtype=8, **dims))
+            m.init_synthetic_weights(); m.init_kv_cache(); m.fill_kv_cache_synthetic(99); m.build_compute_graph(capture_acts=False, fused=False)
+            gp = ((1 + 7919 * np.arange(T)) % V).astype(np.int32)
+            for _ in range(3):
+                m.prefill(gp, 0)
+            G.sync()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                m.prefill(gp, 0)
+            G.sync()
+            gpf = (time.perf_counter() - t0) / reps
+            L.ggb_prof_enable(1)
+            G.prof_reset()
+            m.prefill(gp, 0)
+            G.sync()
+            g_gemm, g_attn = G.prof_get("op_mul_mat")[0], G.prof_get("op_attn")[0]
+            L.ggb_prof_enable(0)
+            g_flops = m.prefill_gemm_flops
+            m.fill_kv_cache_synthetic(99)
+            m.set_state(1, ctx - 1, 0); m.run_steps(8); G.sync()
+            t0 = time.perf_counter()
+            m.run_steps(n_dec); G.sync()
+            gdec = (time.perf_counter() - t0) / n_dec
+            G.prof_reset()
+            m.run_steps_profiled(8)
+            G.sync()
+            g_mv, g_at = G.prof_get("op_mul_mat")[0] / 8, G.prof_get("op_attn")[0] / 8
+            gbytes = m.weight_bytes
+            rec["gemma_equal_size"] = {
+                "config": dict(dims, wtype="q8_0", lowering="per-operator graph"),
+                "prefill": {"tokens_per_s": T / gpf, "ms": 1e3 * gpf, "gemm_ms": g_gemm, "attn_ms": g_attn, "gemm_tflops": g_flops / (g_gemm / 1e3) / 1e12,
+                            "gemm_frac_of_tensor_peak": g_flops / (g_gemm / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                            "attn_tflops_cuda_cores": 4.0 * nl * H * dims["head_dim"] * T * (T + 1) / 2 / (g_attn / 1e3) / 1e12},
+                "decode": {"tokens_per_s": 1.0 / gdec, "us_per_token": 1e6 * gdec, "matvec_us": 1e3 * g_mv, "attn_us": 1e3 * g_at,
+                           "matvec_gbs": gbytes / (g_mv / 1e3) / 1e9, "matvec_frac_of_hbm_peak": gbytes / (g_mv / 1e3) / 1e9 / peaks["hbm_gbs"],
+                           "attn_gbs": 2.0 * 2 * nl * ctx * H * dims["head_dim"] / (g_at / 1e3) / 1e9},
+            }
+            m.close()
+        records[size] = rec
+    first = records[args.sizes.split(",")[0]]
+    print(json.dumps({"metric": "safolorn decode tokens/s", "value": first["decode"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": n_dec, "warmup": 8, "ms_per_step": first["decode"]["us_per_token"] / 1e3, "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random bf16 weights of the configured sizes)",
+                      "config": {"workload": "Safolorn sizes " + args.sizes + ": prefill of %d tokens, greedy decode at n_kv %d, through the serving engine" % (T, ctx),
+                                 "l2": "weights of every size exceed the 126 MB L2"},
+                      "peaks": peaks, "sizes": records}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn"],
+                    help="gemma: the headline workload (default); safolorn: throughput of the Safolorn design beside Gemma at equal size")
+    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn: which of the sizes s, m, l to run")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
@@ -589,6 +755,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.arch == "safolorn":
+        run_safolorn(args)
     elif args.mode == "prefill":
         run_prefill(args)
     else:

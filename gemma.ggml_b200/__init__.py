@@ -179,7 +179,7 @@ _HOST_SIG = {
     "lm_engine_generate": (i32, [vp, C.c_char_p, vp, i32, i32, vp]),
     "lm_engine_stats": (i32, [vp, P(i64)]), "lm_engine_seq_len": (i64, [vp, C.c_char_p]),
     "lm_engine_seq_pages": (i32, [vp, C.c_char_p, vp, i32]),
-    "lm_engine_capture": (i32, [vp, i32]), "lm_engine_get_capture": (i32, [vp, i32, vp, i64]),
+    "lm_engine_capture": (i32, [vp, i32]), "lm_engine_use_graphs": (i32, [vp, i32]), "lm_engine_get_capture": (i32, [vp, i32, vp, i64]),
     "lm_architectures_csv": (i32, [C.c_char_p, i32]),
     "sf_config_probe": (i32, [C.c_char_p, P(i64)]),
     "st_probe": (i32, [C.c_char_p, C.c_char_p, P(i64), P(i64), C.c_char_p, i32, P(i64)]),
@@ -719,6 +719,10 @@ class Engine:
 
     def capture(self, on=True):
         self._check(host_lib().lm_engine_capture(self.h, 1 if on else 0), "capture")
+
+    def use_graphs(self, on=True):
+        """one-token steps as replayed CUDA graphs (default) or as eager launches (per-operator probes)"""
+        self._check(host_lib().lm_engine_use_graphs(self.h, 1 if on else 0), "use_graphs")
 
     def captured(self, layer, tokens, width):
         """Residual stream after `layer` of the last forward call: float32 [tokens, width]."""

@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
         uint4 raw[kStages][PBW];
         __half dd[kStages];
         auto fetch = [&](int kb, uint4 (&r)[PBW], __half &d1) {
-            if (!wlive || kb >= kb1) return;
+            if (TYPE == GGB_TYPE_BF16 || !wlive || kb >= kb1) return;
             const size_t blk = (size_t)wrow * A.nb + (size_t)kb * 2 + whalf;
             d1 = sg.d[blk];
             const uint4 *src = reinterpret_cast<const uint4 *>(sg.qs + blk * (TYPE == GGB_TYPE_Q8_0 ? 32 : 16));
@@ -239,7 +239,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
                         }
                     }
                 }
-                // W tile: convert the block requested kStages K blocks ago, then request block kb + kStages
+                // W tile.  Plain bf16 matrix: the same copy as the A tile (rows of the matrix are K-major already)
+                if (TYPE == GGB_TYPE_BF16) {
+                    const int ch = tid & 7;
+                    const __nv_bfloat16 *wm = reinterpret_cast<const __nv_bfloat16 *>(sg.qs);
+#pragma unroll
+                    for (int r = tid >> 3; r < BN; r += kProducerThreads / 8) {
+                        const int row = sn0 + r;
+                        const uint32_t dst = sb + r * 128 + ((ch ^ (r & 7)) << 4);
+                        if (row < sg.rows) {
+                            const void *src = reinterpret_cast<const uint4 *>(wm + (size_t)row * A.K + (size_t)kb * BK) + ch;
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                        } else {
+                            sts_u4(dst, make_uint4(0, 0, 0, 0));
+                        }
+                    }
+                } else
+                // quantised matrix: convert the block requested kStages K blocks ago, then request block kb + kStages
                 {
                     uint4 cur[PBW];
 #pragma unroll
@@ -730,7 +746,7 @@ static int gemm_launch(int n, const ggb_weight *const *w, const void *a_bf16, in
     GGB_CHECK_ARG(n == 1 || !resid, "gemm: a residual needs a single matrix");
     const int64_t K = w[0]->cols;
     const int type = w[0]->type;
-    GGB_CHECK_ARG(type == GGB_TYPE_Q4_0 || type == GGB_TYPE_Q8_0, "gemm: weight type %d", type);
+    GGB_CHECK_ARG(type == GGB_TYPE_Q4_0 || type == GGB_TYPE_Q8_0 || type == GGB_TYPE_BF16, "gemm: weight type %d", type);
     GemmArgs A{};
     int64_t N = 0;
     for (int i = 0; i < n; i++) {
@@ -746,6 +762,7 @@ static int gemm_launch(int n, const ggb_weight *const *w, const void *a_bf16, in
     if (!attr_done) {
         GGB_CUDA(cudaFuncSetAttribute(gemm_bf16w_kernel<GGB_TYPE_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
         GGB_CUDA(cudaFuncSetAttribute(gemm_bf16w_kernel<GGB_TYPE_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+        GGB_CUDA(cudaFuncSetAttribute(gemm_bf16w_kernel<GGB_TYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
         attr_done = true;
     }
     const int n_tiles = (int)((N + BN - 1) / BN), m_tiles = (int)((T + BM - 1) / BM), kblocks = (int)(K / BK);
@@ -762,6 +779,7 @@ static int gemm_launch(int n, const ggb_weight *const *w, const void *a_bf16, in
     const dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
     if (splits > 1) A.resid = nullptr; // added by the reducer
     if (type == GGB_TYPE_Q4_0) gemm_bf16w_kernel<GGB_TYPE_Q4_0><<<grid, kGemmThreads, kGemmSmem, ggb_cuda_stream()>>>(A);
+    else if (type == GGB_TYPE_BF16) gemm_bf16w_kernel<GGB_TYPE_BF16><<<grid, kGemmThreads, kGemmSmem, ggb_cuda_stream()>>>(A);
     else gemm_bf16w_kernel<GGB_TYPE_Q8_0><<<grid, kGemmThreads, kGemmSmem, ggb_cuda_stream()>>>(A);
     GGB_LAUNCH_CHECK();
     if (splits > 1) {
@@ -823,6 +841,32 @@ int ggb_op_attn_prefill(const float *q, const void *kcache, const void *vcache, 
 
 } // extern "C"
 
-// the GEMM on plain bf16 matrices (both operands copied by cp.async, nothing to dequantise)
-bool ggb_gemm_dense_bf16_fits(int64_t N, int64_t K, int64_t T, int64_t ldc) { return false; }
-int ggb_gemm_dense_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t T, float *c, int64_t ldc) { return GGB_ERR_UNSUPPORTED; }
+// the GEMM on plain bf16 matrices (both operands copied by cp.async, nothing to dequantise): the matrix is described
+// as a ggb_weight of type BF16 whose payload plane is the matrix itself.  The K-split workspace belongs to the library
+// and only grows.
+bool ggb_gemm_dense_bf16_fits(int64_t N, int64_t K, int64_t T, int64_t ldc) {
+    return T >= 64 && K % 64 == 0 && N % 32 == 0 && ldc % 4 == 0 && N < (1ll << 31) && K < (1ll << 31) && T < (1ll << 31);
+}
+int ggb_gemm_dense_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t T, float *c, int64_t ldc) {
+    GGB_REQUIRE_INIT();
+    static void *ws = nullptr;
+    static size_t ws_bytes = 0;
+    const int n_tiles = (int)((N + BN - 1) / BN), m_tiles = (int)((T + BM - 1) / BM);
+    if (n_tiles * m_tiles * 2 <= ggb_sm_count()) { // small enough to be split along K
+        const size_t need = ggb_gemm_workspace_bytes(T, N, K);
+        if (need > ws_bytes) {
+            if (ws) cudaFree(ws);
+            ws = nullptr, ws_bytes = 0;
+            GGB_CUDA(cudaMalloc(&ws, need));
+            ws_bytes = need;
+        }
+    }
+    ggb_weight wd{};
+    wd.type = GGB_TYPE_BF16;
+    wd.rows = N, wd.cols = K, wd.nb = K / 32;
+    wd.qs = reinterpret_cast<uint8_t *>(const_cast<void *>(w));
+    const ggb_weight *wp[1] = {&wd};
+    float *cs[1] = {c};
+    const int64_t ls[1] = {ldc};
+    return gemm_launch(1, wp, a, T, cs, ls, nullptr, ws, ws_bytes);
+}

@@ -195,6 +195,12 @@ int lm_engine_capture(void *e, int on) {
     sf->set_capture(on != 0);
     return 0;
 }
+int lm_engine_use_graphs(void *e, int on) {
+    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
+    if (!sf) return -1;
+    sf->set_use_graphs(on != 0);
+    return 0;
+}
 int lm_engine_get_capture(void *e, int layer, float *host, int64_t n) {
     safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
     return sf ? sf->get_capture(layer, host, n) : -1;

@@ -3,9 +3,19 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "seq_cache.h"
+
+// an operator under the library's cudaEvent probes (ggb_prof_*), keyed by operator class like the Gemma path
+#define SF_OP(name, expr)                              \
+    do {                                               \
+        ggb_prof_start(name);                          \
+        const int rc__ = (expr);                       \
+        ggb_prof_stop(name);                           \
+        if (rc__ != 0) return fail(rc__, #expr);       \
+    } while (0)
 
 #define SF_TRY(expr)                                   \
     do {                                               \
@@ -366,8 +376,8 @@ safolorn_model *safolorn_model::create_random(const sf_config &cfg, const lm_loa
 }
 
 void safolorn_model::free_all() {
-    if (graph1_) ggb_graph_free(graph1_);
-    graph1_ = nullptr;
+    for (step_graph &g : graphs_) ggb_graph_free(g.graph);
+    graphs_.clear();
     for (void *p : owned_) ggb_buffer_free(p);
     owned_.clear();
 }
@@ -460,7 +470,7 @@ int safolorn_model::emit(int T, int ns, const int32_t *table, int n_want) {
     const sf_config &c = cfg_;
     const int64_t W = c.width, t = T;
     const int B = cache_->page_size();
-    SF_TRY(ggb_op_embed_rows(dt_, embed_, ids_, t, W, x_));
+    SF_OP("op_rows", ggb_op_embed_rows(dt_, embed_, ids_, t, W, x_));
     for (size_t li = 0; li < c.layers.size(); li++) {
         const sf_layer_cfg &l = c.layers[li];
         const sf_layer_w &w = lw_[li];
@@ -468,33 +478,33 @@ int safolorn_model::emit(int T, int ns, const int32_t *table, int n_want) {
         const int64_t Nq = (int64_t)H * (D + Dr), Nqd = Nq + (l.kv_from < 0 ? R + Dr : 0);
         void *cache = cache_->layer(w.cache_index);
         // both branches norm the same x: one pass, two weights
-        SF_TRY(ggb_op_rms_norm2(dt_, x_, W, w.norm1, w.norm1_stride, w.norm2, w.norm2_stride, c.eps, W, t, h1_, l.mlp ? h2_ : nullptr));
-        SF_TRY(ggb_op_linear(dt_, w.qd, Nqd, W, h1_, W, t, qd_, Nqd));
+        SF_OP("op_norm", ggb_op_rms_norm2(dt_, x_, W, w.norm1, w.norm1_stride, w.norm2, w.norm2_stride, c.eps, W, t, h1_, l.mlp ? h2_ : nullptr));
+        SF_OP("op_linear", ggb_op_linear(dt_, w.qd, Nqd, W, h1_, W, t, qd_, Nqd));
         if (l.kv_from < 0)
-            SF_TRY(ggb_op_latent_kv_store(dt_, qd_ + Nq, Nqd, t, R, Dr, l.rot.dims, w.dkv_norm, c.eps, w.cos_sin, pos0_, table, B, cache));
-        SF_TRY(ggb_op_latent_q_absorb(dt_, qd_, Nqd, t, H, D, Dr, l.rot.dims, w.cos_sin, pos0_, w.uk, R, l.scale, qa_));
-        SF_TRY(ggb_op_latent_attn(dt_, qa_, cache, table, B, pos0_, t, H, R, Dr, ns, part_));
-        SF_TRY(ggb_op_latent_attn_out(dt_, part_, ns, w.sink, w.uv, t, H, R, Dv, ao_));
-        SF_TRY(ggb_op_linear(dt_, w.o, W, (int64_t)H * Dv, ao_, (int64_t)H * Dv, t, attn_o_, W));
+            SF_OP("op_attn_prep", ggb_op_latent_kv_store(dt_, qd_ + Nq, Nqd, t, R, Dr, l.rot.dims, w.dkv_norm, c.eps, w.cos_sin, pos0_, table, B, cache));
+        SF_OP("op_attn_prep", ggb_op_latent_q_absorb(dt_, qd_, Nqd, t, H, D, Dr, l.rot.dims, w.cos_sin, pos0_, w.uk, R, l.scale, qa_));
+        SF_OP("op_attn", ggb_op_latent_attn(dt_, qa_, cache, table, B, pos0_, t, H, R, Dr, ns, part_));
+        SF_OP("op_attn_out", ggb_op_latent_attn_out(dt_, part_, ns, w.sink, w.uv, t, H, R, Dv, ao_));
+        SF_OP("op_linear", ggb_op_linear(dt_, w.o, W, (int64_t)H * Dv, ao_, (int64_t)H * Dv, t, attn_o_, W));
         if (l.mlp == 1) {
-            SF_TRY(ggb_op_linear(dt_, w.gate_up, 2 * (int64_t)l.ff, W, h2_, W, t, gu_, 2 * (int64_t)l.ff));
-            SF_TRY(ggb_op_glu_clamp(dt_, gu_, l.ff, t, l.limit, 1.702f, act_));
-            SF_TRY(ggb_op_linear(dt_, w.down, W, l.ff, act_, l.ff, t, ff_o_, W));
+            SF_OP("op_linear", ggb_op_linear(dt_, w.gate_up, 2 * (int64_t)l.ff, W, h2_, W, t, gu_, 2 * (int64_t)l.ff));
+            SF_OP("op_act", ggb_op_glu_clamp(dt_, gu_, l.ff, t, l.limit, 1.702f, act_));
+            SF_OP("op_linear", ggb_op_linear(dt_, w.down, W, l.ff, act_, l.ff, t, ff_o_, W));
         } else if (l.mlp == 2) {
-            SF_TRY(ggb_op_moe_route(dt_, h2_, W, t, w.router, w.router_b, l.experts, l.top, route_i_, route_w_));
-            SF_TRY(ggb_op_moe_group(route_i_, t, l.top, l.experts, group_ws_));
-            SF_TRY(ggb_op_moe_linear(dt_, w.e_up, l.ff, W, h2_, W, 1, t, l.top, l.experts, group_ws_, 1, y1_, l.ff));
-            SF_TRY(ggb_op_moe_linear(dt_, w.e_down, W, l.ff, y1_, l.ff, 0, t, l.top, l.experts, group_ws_, 0, y2_, W));
-            SF_TRY(ggb_op_moe_combine(y2_, group_ws_, route_w_, t, l.top, l.experts, W, ff_o_));
+            SF_OP("op_moe", ggb_op_moe_route(dt_, h2_, W, t, w.router, w.router_b, l.experts, l.top, route_i_, route_w_));
+            SF_OP("op_moe", ggb_op_moe_group(route_i_, t, l.top, l.experts, group_ws_));
+            SF_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_up, l.ff, W, h2_, W, 1, t, l.top, l.experts, group_ws_, 1, y1_, l.ff));
+            SF_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_down, W, l.ff, y1_, l.ff, 0, t, l.top, l.experts, group_ws_, 0, y2_, W));
+            SF_OP("op_moe", ggb_op_moe_combine(y2_, group_ws_, route_w_, t, l.top, l.experts, W, ff_o_));
         }
-        SF_TRY(ggb_op_residual_side(dt_, x_, attn_o_, l.mlp ? ff_o_ : nullptr, W, t, ids_, side_embed_, (int64_t)c.layers.size() * c.side_dim,
+        SF_OP("op_residual", ggb_op_residual_side(dt_, x_, attn_o_, l.mlp ? ff_o_ : nullptr, W, t, ids_, side_embed_, (int64_t)c.layers.size() * c.side_dim,
                                     (int64_t)li * c.side_dim, c.side_dim, w.side_gate, w.side_proj, w.side_norm, c.eps));
-        if (capture_ && cap_) SF_TRY(ggb_op_gather_rows_f32(x_, want_ + max_T_, t, W, cap_ + (size_t)li * (size_t)max_T_ * (size_t)W));
+        if (capture_ && cap_) SF_OP("op_rows", ggb_op_gather_rows_f32(x_, want_ + max_T_, t, W, cap_ + (size_t)li * (size_t)max_T_ * (size_t)W));
     }
     if (n_want > 0) {
-        SF_TRY(ggb_op_gather_rows_f32(x_, want_, n_want, W, xw_));
-        SF_TRY(ggb_op_rms_norm2(dt_, xw_, W, final_norm_, final_norm_stride_, nullptr, 0, c.eps, W, n_want, hw_, nullptr));
-        SF_TRY(ggb_op_linear(dt_, head_, c.vocab, W, hw_, W, n_want, logits_, c.vocab));
+        SF_OP("op_rows", ggb_op_gather_rows_f32(x_, want_, n_want, W, xw_));
+        SF_OP("op_norm", ggb_op_rms_norm2(dt_, xw_, W, final_norm_, final_norm_stride_, nullptr, 0, c.eps, W, n_want, hw_, nullptr));
+        SF_OP("op_linear", ggb_op_linear(dt_, head_, c.vocab, W, hw_, W, n_want, logits_, c.vocab));
     }
     return 0;
 }
@@ -518,6 +528,11 @@ int safolorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
     const int64_t n_kv = p.pos0 + p.T;
     int64_t ns = std::min<int64_t>((n_kv + 127) / 128, std::max<int64_t>(1, 296 / p.T));
     ns = std::max<int64_t>(1, std::min<int64_t>(ns, 64));
+    if (p.T == 1) { // powers of two: the captured one-token step changes rarely
+        int64_t q = 1;
+        while (q < ns) q *= 2;
+        ns = q;
+    }
     while (ns > 1 && ns * p.T > part_rows_) ns--;
     const int64_t l0 = ggb_launch_count();
     if (capture_) {
@@ -538,7 +553,26 @@ int safolorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
         }
         cap_T_ = p.T;
     }
-    SF_TRY(emit(p.T, (int)ns, p.block_table_dev, n_want));
+    if (p.T == 1 && use_graphs_ && !capture_ && !getenv("GGB_SF_NO_GRAPH")) {
+        ggb_graph *g = nullptr;
+        for (const step_graph &sg : graphs_)
+            if (sg.table == p.block_table_dev && sg.n_split == (int)ns && sg.n_want == n_want) g = sg.graph;
+        if (!g) {
+            SF_TRY(ggb_capture_begin());
+            const int rc = emit(1, (int)ns, p.block_table_dev, n_want);
+            const int rc2 = ggb_capture_end(&g);
+            if (rc) return rc;
+            if (rc2) return fail(rc2, "ggb_capture_end");
+            if (graphs_.size() >= 32) {
+                ggb_graph_free(graphs_.front().graph);
+                graphs_.erase(graphs_.begin());
+            }
+            graphs_.push_back(step_graph{p.block_table_dev, (int)ns, n_want, g});
+        }
+        SF_TRY(ggb_graph_launch(g));
+    } else {
+        SF_TRY(emit(p.T, (int)ns, p.block_table_dev, n_want));
+    }
     kernels_last_ = (int)(ggb_launch_count() - l0);
     return 0;
 }

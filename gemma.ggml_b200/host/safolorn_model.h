@@ -80,6 +80,7 @@ class safolorn_model : public lm_model {
     const sf_config &config() const { return cfg_; }
     // keep the residual stream after every layer of the next forward calls (fp32 [layers][T][width] of the last portion)
     void set_capture(bool on) { capture_ = on; }
+    void set_use_graphs(bool on) { use_graphs_ = on; }
     int get_capture(int layer, float *host, int64_t n) const;
     size_t weight_bytes() const { return weight_bytes_; }
     int kernels_last_forward() const { return kernels_last_; }
@@ -118,7 +119,13 @@ class safolorn_model : public lm_model {
     bool capture_ = false;
     int cap_T_ = 0;
     int kernels_last_ = 0;
-    // the one-token step as a CUDA graph (replayed while the page-table length class and n_split stay the same)
-    ggb_graph *graph1_ = nullptr;
-    int graph1_split_ = 0, graph1_want_ = -1;
+    // the one-token step as CUDA graphs: position and pages are read on the device, so one graph serves a sequence
+    // until the number of splits of its visible positions changes (powers of two)
+    struct step_graph {
+        const int32_t *table;
+        int n_split, n_want;
+        ggb_graph *graph;
+    };
+    std::vector<step_graph> graphs_;
+    bool use_graphs_ = true;
 };
