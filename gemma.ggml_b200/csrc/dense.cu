@@ -186,48 +186,107 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
 }
 
 // x <- x + a (+ f); then, with a side input, x <- x + rms(y) * nw, y = proj (gelu_tanh(gate x) * e), e = the token's
-// slice [e_off, e_off + sd) of its side-embedding row.  One CTA per token; x is staged in shared memory (fp32).
-template <typename E>
-__global__ void __launch_bounds__(256) residual_side_kernel(float *__restrict__ x, const float *__restrict__ a, const float *__restrict__ f,
-                                                            int64_t W, const int32_t *__restrict__ ids, const E *__restrict__ side_embed,
-                                                            int64_t e_ld, int64_t e_off, int sd, const E *__restrict__ w_gate,
-                                                            const E *__restrict__ w_proj, const float *__restrict__ nw, float eps) {
+// slice [e_off, e_off + sd) of its side-embedding row.  A CTA takes TT tokens (x staged in shared memory, fp32) so that
+// the two small matrices are read once for all of them; rows are read with 16-byte loads, several in flight.
+template <typename E> struct Vec16 {
+    static constexpr int n = 16 / (int)sizeof(E);
+    uint4 raw;
+    __device__ __forceinline__ float at(int i) const { return to_f32(reinterpret_cast<const E *>(&raw)[i]); }
+};
+
+template <typename E, int TT>
+__global__ void __launch_bounds__(512) residual_side_kernel(float *__restrict__ x, const float *__restrict__ a, const float *__restrict__ f,
+                                                            int64_t W, int64_t T, const int32_t *__restrict__ ids,
+                                                            const E *__restrict__ side_embed, int64_t e_ld, int64_t e_off, int sd,
+                                                            const E *__restrict__ w_gate, const E *__restrict__ w_proj,
+                                                            const float *__restrict__ nw, float eps, int vec) {
     extern __shared__ float rs_smem[];
-    float *xs = rs_smem, *ys = xs + W, *gs = ys + W;
-    __shared__ float red[8];
-    const int64_t t = blockIdx.x;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float *xr = x + t * W;
-    for (int64_t i = tid; i < W; i += blockDim.x) {
-        float v = xr[i] + (f ? a[t * W + i] + f[t * W + i] : a[t * W + i]);
+    float *xs = rs_smem, *ys = xs + TT * W, *gs = ys + TT * W; // [TT][W], [TT][W], [TT][sd]
+    __shared__ float red[TT][16];
+    constexpr int VN = Vec16<E>::n;
+    const int64_t t0 = (int64_t)blockIdx.x * TT;
+    const int nt = (int)min((int64_t)TT, T - t0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    for (int64_t i = tid; i < (int64_t)TT * W; i += blockDim.x) {
+        const int tt = (int)(i / W);
+        float v = 0.f;
+        if (tt < nt) {
+            const int64_t g = t0 * W + i;
+            v = x[g] + (f ? a[g] + f[g] : a[g]);
+            if (!sd) x[g] = v;
+        }
         xs[i] = v;
-        if (!sd) xr[i] = v;
     }
     if (!sd) return;
     __syncthreads();
-    const E *e = side_embed + (int64_t)ids[t] * e_ld + e_off;
-    for (int i = warp; i < sd; i += 8) {
-        float s = 0.f;
-        for (int64_t k = lane; k < W; k += 32) s = fmaf(to_f32(w_gate[(int64_t)i * W + k]), xs[k], s);
-        s = warp_sum_f32(s);
-        if (lane == 0) gs[i] = gelu_tanh_f32(s) * to_f32(e[i]);
-    }
-    __syncthreads();
-    float ss = 0.f;
-    for (int64_t i = tid; i < W; i += blockDim.x) {
-        float s = 0.f;
-        for (int k = 0; k < sd; k++) s = fmaf(to_f32(w_proj[i * sd + k]), gs[k], s);
-        ys[i] = s;
-        ss = fmaf(s, s, ss);
-    }
-    ss = warp_sum_f32(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    float tot = 0.f;
+    for (int i = warp; i < sd; i += nwarp) { // gate: a warp per output, the row of w_gate read once for the TT tokens
+        float s[TT];
 #pragma unroll
-    for (int i = 0; i < 8; i++) tot += red[i];
-    const float r = 1.0f / sqrtf(tot / (float)W + eps);
-    for (int64_t i = tid; i < W; i += blockDim.x) xr[i] = xs[i] + ys[i] * r * nw[i];
+        for (int tt = 0; tt < TT; tt++) s[tt] = 0.f;
+        const E *wr = w_gate + (int64_t)i * W;
+        if (vec) {
+#pragma unroll 4
+            for (int64_t k = (int64_t)lane * VN; k < W; k += 32 * VN) {
+                Vec16<E> v;
+                v.raw = *reinterpret_cast<const uint4 *>(wr + k);
+#pragma unroll
+                for (int u = 0; u < VN; u++)
+#pragma unroll
+                    for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(v.at(u), xs[tt * W + k + u], s[tt]);
+            }
+        } else {
+            for (int64_t k = lane; k < W; k += 32)
+#pragma unroll
+                for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(to_f32(wr[k]), xs[tt * W + k], s[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            const float r = warp_sum_f32(s[tt]);
+            if (lane == 0 && tt < nt) gs[tt * sd + i] = gelu_tanh_f32(r) * to_f32(side_embed[(int64_t)ids[t0 + tt] * e_ld + e_off + i]);
+        }
+    }
+    __syncthreads();
+    float ss[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; tt++) ss[tt] = 0.f;
+    for (int64_t i = tid; i < W; i += blockDim.x) { // proj: a thread per output, its row of sd numbers in 16-byte pieces
+        float s[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) s[tt] = 0.f;
+        const E *wr = w_proj + i * sd;
+        if (vec) {
+#pragma unroll 8
+            for (int k = 0; k < sd; k += VN) {
+                Vec16<E> v;
+                v.raw = *reinterpret_cast<const uint4 *>(wr + k);
+#pragma unroll
+                for (int u = 0; u < VN; u++)
+#pragma unroll
+                    for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(v.at(u), gs[tt * sd + k + u], s[tt]);
+            }
+        } else {
+            for (int k = 0; k < sd; k++)
+#pragma unroll
+                for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(to_f32(wr[k]), gs[tt * sd + k], s[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            ys[tt * W + i] = s[tt];
+            ss[tt] = fmaf(s[tt], s[tt], ss[tt]);
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; tt++) {
+        const float r = warp_sum_f32(ss[tt]);
+        if (lane == 0) red[tt][warp] = r;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+        float tot = 0.f;
+        for (int i = 0; i < nwarp; i++) tot += red[tt][i];
+        const float r = 1.0f / sqrtf(tot / (float)W + eps);
+        for (int64_t i = tid; i < W; i += blockDim.x) x[(t0 + tt) * W + i] = xs[tt * W + i] + ys[tt * W + i] * r * nw[i];
+    }
 }
 
 template <typename E>
@@ -338,19 +397,32 @@ int ggb_op_residual_side(int dt, float *x, const float *a, const float *f, int64
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(x && a && W > 0 && T > 0 && sd >= 0, "residual_side: bad arguments");
     GGB_CHECK_ARG(!sd || (ids && side_embed && w_gate && w_proj && nw), "residual_side: a side input needs its tensors");
-    const size_t smem = (size_t)(2 * W + sd) * sizeof(float);
-    GGB_CHECK_ARG(smem <= 200 * 1024, "residual_side: width %lld does not fit shared memory", (long long)W);
-    if (dt == GGB_TYPE_BF16) {
-        auto k = residual_side_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(x, a, f, W, ids, (const __nv_bfloat16 *)side_embed, e_ld, e_off, sd,
-                                                        (const __nv_bfloat16 *)w_gate, (const __nv_bfloat16 *)w_proj, nw, eps);
-    } else {
-        auto k = residual_side_kernel<float>;
-        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(x, a, f, W, ids, (const float *)side_embed, e_ld, e_off, sd, (const float *)w_gate,
-                                                        (const float *)w_proj, nw, eps);
+    // tokens per CTA: as many as shared memory holds (up to 8), one when there are too few tokens to fill the GPU
+    const size_t per_token = (size_t)(2 * W + sd) * sizeof(float);
+    GGB_CHECK_ARG(per_token <= 200 * 1024, "residual_side: width %lld does not fit shared memory", (long long)W);
+    int tt = 8;
+    while (tt > 1 && (per_token * tt > 96 * 1024 || T < (int64_t)tt * 64)) tt >>= 1;
+    const size_t smem = per_token * tt;
+    const int vn = dt == GGB_TYPE_BF16 ? 8 : 4;
+    const int vec = sd && W % vn == 0 && sd % vn == 0 && ((uintptr_t)w_gate | (uintptr_t)w_proj) % 16 == 0;
+    const unsigned grid = (unsigned)((T + tt - 1) / tt);
+#define RS_LAUNCH(E, TT)                                                                                                               \
+    {                                                                                                                                  \
+        auto k = residual_side_kernel<E, TT>;                                                                                          \
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
+        k<<<grid, 512, smem, ggb_cuda_stream()>>>(x, a, f, W, T, ids, (const E *)side_embed, e_ld, e_off, sd, (const E *)w_gate,         \
+                                                  (const E *)w_proj, nw, eps, vec);                                                    \
     }
+#define RS_CASES(E)                          \
+    switch (tt) {                            \
+    case 8: RS_LAUNCH(E, 8) break;           \
+    case 4: RS_LAUNCH(E, 4) break;           \
+    case 2: RS_LAUNCH(E, 2) break;           \
+    default: RS_LAUNCH(E, 1) break;          \
+    }
+    if (dt == GGB_TYPE_BF16) { RS_CASES(__nv_bfloat16) } else { RS_CASES(float) }
+#undef RS_CASES
+#undef RS_LAUNCH
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

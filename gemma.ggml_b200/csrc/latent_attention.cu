@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(256) latent_q_absorb_kernel(const float *__res
 #pragma unroll
         for (int tt = 0; tt < kAbsT; tt++) acc[tt] = 0.f;
         const E *wc = w_uk + (int64_t)h * D * R + r;
+#pragma unroll 8
         for (int dd = 0; dd < D; dd++) {
             const float w = to_f32(wc[(int64_t)dd * R]);
 #pragma unroll
@@ -139,10 +140,8 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
         const int h = h0 + warp;
         const bool live = h < H;
         __syncthreads(); // the previous group's q and tile are no longer read
-        for (int i = threadIdx.x; i < NW * QKp; i += blockDim.x) {
-            const int w = i / QKp, k = i - w * QKp;
-            qsm[i] = (h0 + w < H && k < QK) ? qa[((int64_t)t * H + h0 + w) * QK + k] : 0.f;
-        }
+        for (int k = lane; k < QKp; k += 32) // every warp stages its own head
+            qsm[warp * QKp + k] = (live && k < QK) ? qa[((int64_t)t * H + h) * QK + k] : 0.f;
         float m = -INFINITY, l = 0.f, acc[RC];
 #pragma unroll
         for (int i = 0; i < RC; i++) acc[i] = 0.f;
@@ -150,9 +149,18 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
         for (int64_t j = j0; j < j1; j += 32) {
             __syncthreads();
             const int rows = (int)min((int64_t)32, j1 - j);
-            for (int i = threadIdx.x; i < rows * words; i += blockDim.x) {
-                const int jj = i / words, w = i - jj * words;
-                tile[jj * SW + w] = reinterpret_cast<const uint32_t *>(cache + cache_row(table, B, j + jj) * ldk)[w];
+            // a warp copies whole rows: one page lookup per row, then 16-byte loads that are all in flight together
+            // (cache rows start on 16-byte boundaries: their pitch is a multiple of 8 numbers)
+            for (int jj = warp; jj < rows; jj += NW) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(cache + cache_row(table, B, j + jj) * ldk);
+                uint32_t *dst = tile + jj * SW;
+                for (int w4 = lane; w4 * 4 < words; w4 += 32) {
+                    const uint4 v = src[w4];
+                    dst[w4 * 4] = v.x;
+                    if (w4 * 4 + 1 < words) dst[w4 * 4 + 1] = v.y;
+                    if (w4 * 4 + 2 < words) dst[w4 * 4 + 2] = v.z;
+                    if (w4 * 4 + 3 < words) dst[w4 * 4 + 3] = v.w;
+                }
             }
             __syncthreads();
             if (!live) continue;
@@ -206,22 +214,31 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
     const int64_t t0 = (int64_t)blockIdx.x * kOutT;
     const int nt = (int)min((int64_t)kOutT, T - t0);
     const float sk = sink[h];
+    float *wsm = ol + kOutT * R; // [kOutT][n_split] weight of every split: exp(m_s - M) / L
+    const int64_t ps = (int64_t)H * (R + 2);
+    if (warp < nt) { // one warp per token: maximum and denominator over the splits and the sink
+        const float *p0 = part + (((t0 + warp) * n_split) * H + h) * (R + 2);
+        float M = sk;
+        for (int s = lane; s < n_split; s += 32) M = fmaxf(M, p0[s * ps]);
+        M = warp_max_f32(M);
+        float L = 0.f;
+        for (int s = lane; s < n_split; s += 32) L = fmaf(p0[s * ps + 1], expf(p0[s * ps] - M), L);
+        L = warp_sum_f32(L) + expf(sk - M);
+        const float inv = 1.0f / L;
+        for (int s = lane; s < n_split; s += 32) wsm[warp * n_split + s] = expf(p0[s * ps] - M) * inv;
+    }
+    __syncthreads();
     for (int tt = 0; tt < kOutT; tt++) {
         if (tt >= nt) {
             for (int r = tid; r < R; r += 256) ol[tt * R + r] = 0.f;
             continue;
         }
-        const float *p0 = part + (((t0 + tt) * n_split) * H + h) * (R + 2);
-        const int64_t ps = (int64_t)H * (R + 2);
-        float M = sk;
-        for (int s = 0; s < n_split; s++) M = fmaxf(M, p0[s * ps]);
-        float L = expf(sk - M);
-        for (int s = 0; s < n_split; s++) L = fmaf(p0[s * ps + 1], expf(p0[s * ps] - M), L);
-        const float inv = 1.0f / L;
+        const float *p0 = part + (((t0 + tt) * n_split) * H + h) * (R + 2) + 2;
         for (int r = tid; r < R; r += 256) {
             float a = 0.f;
-            for (int s = 0; s < n_split; s++) a = fmaf(p0[s * ps + 2 + r], expf(p0[s * ps] - M), a);
-            ol[tt * R + r] = a * inv;
+#pragma unroll 8
+            for (int s = 0; s < n_split; s++) a = fmaf(p0[s * ps + r], wsm[tt * n_split + s], a);
+            ol[tt * R + r] = a;
         }
     }
     __syncthreads();
@@ -230,6 +247,7 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
         float acc[kOutT];
 #pragma unroll
         for (int tt = 0; tt < kOutT; tt++) acc[tt] = 0.f;
+#pragma unroll 4
         for (int k = lane; k < R; k += 32) {
             const float w = to_f32(wr[k]);
 #pragma unroll
@@ -336,8 +354,8 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(part && sink && w_uv && out && T > 0 && H > 0 && R > 0 && Dv > 0 && n_split > 0, "latent_attn_out: bad arguments");
     const dim3 grid((unsigned)((T + kOutT - 1) / kOutT), (unsigned)H);
-    const size_t smem = (size_t)kOutT * R * 4;
-    GGB_CHECK_ARG(smem <= 48 * 1024, "latent_attn_out: latent size %d too large", R);
+    const size_t smem = (size_t)kOutT * (R + n_split) * 4;
+    GGB_CHECK_ARG(smem <= 48 * 1024, "latent_attn_out: latent size %d with %d splits too large", R, n_split);
     if (dt == GGB_TYPE_BF16)
         latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const __nv_bfloat16 *)w_uv, T, H, R, Dv,
                                                                        (__nv_bfloat16 *)out);

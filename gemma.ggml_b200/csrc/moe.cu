@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const E *__restrict__ h,
     const E *hr = h + t * W;
     for (int e = warp; e < n_exp; e += 4) {
         float s = 0.f;
+#pragma unroll 8
         for (int64_t k = lane; k < W; k += 32) s = fmaf(w[(int64_t)e * W + k], to_f32(hr[k]), s);
         s = warp_sum_f32(s);
         if (lane == 0) z[e] = s + (b ? b[e] : 0.f);
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const E *__restrict__ h,
 // one CTA: counts per expert, offsets, the list of 64-row tiles, and the sorted order of the n = T * top slots
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ idx, int n, int top, int n_exp, int32_t *offsets,
                                                          int32_t *row_src, int32_t *inv, int32_t *tile_expert, int32_t *tile_row0,
-                                                         int32_t *n_tiles) {
+                                                         int32_t *n_tiles, int32_t *row_expert) {
     extern __shared__ int32_t cnt[]; // [n_exp] counts, then cursors
     for (int e = threadIdx.x; e < n_exp; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
@@ -87,7 +88,39 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restri
     for (int s = threadIdx.x; s < n; s += blockDim.x) {
         const int p = atomicAdd(&cnt[idx[s]], 1);
         row_src[p] = s / top;
+        row_expert[p] = idx[s];
         inv[s] = p;
+    }
+}
+
+// few slots (decode): a warp per (sorted row, output) streams the expert's weight row with 16-byte loads
+template <typename E, int ACT>
+__global__ void __launch_bounds__(256) moe_vec_kernel(const E *__restrict__ w, int64_t N, int64_t K, const E *__restrict__ a, int64_t lda,
+                                                      const int32_t *__restrict__ row_src, const int32_t *__restrict__ row_expert,
+                                                      float *__restrict__ c, E *__restrict__ c_act, int64_t ldc, int vec) {
+    constexpr int VE = 16 / (int)sizeof(E);
+    const int lane = threadIdx.x & 31;
+    const int64_t n = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int row = blockIdx.y;
+    if (n >= N) return;
+    const E *wr = w + ((int64_t)row_expert[row] * N + n) * K;
+    const E *ar = a + (int64_t)(row_src ? row_src[row] : row) * lda;
+    float acc = 0.f;
+    if (vec) {
+#pragma unroll 4
+        for (int64_t k = (int64_t)lane * VE; k < K; k += 32 * VE) {
+            const uint4 wv = ldg_stream_u4(wr + k), av = *reinterpret_cast<const uint4 *>(ar + k);
+            const E *we = reinterpret_cast<const E *>(&wv), *ae = reinterpret_cast<const E *>(&av);
+#pragma unroll
+            for (int u = 0; u < VE; u++) acc = fmaf(to_f32(we[u]), to_f32(ae[u]), acc);
+        }
+    } else {
+        for (int64_t k = lane; k < K; k += 32) acc = fmaf(to_f32(wr[k]), to_f32(ar[k]), acc);
+    }
+    acc = warp_sum_f32(acc);
+    if (lane == 0) {
+        if (ACT == 1) c_act[(int64_t)row * ldc + n] = from_f32<E>(acc > 0.f ? acc * acc : 0.f);
+        else c[(int64_t)row * ldc + n] = acc;
     }
 }
 
@@ -124,7 +157,7 @@ int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w
 
 int ggb_moe_max_tiles(int64_t n_slots, int n_exp) { return (int)(n_slots / 64) + n_exp; }
 size_t ggb_moe_group_ints(int64_t n_slots, int n_exp) {
-    return (size_t)(n_exp + 1) + 2 * (size_t)n_slots + 2 * (size_t)ggb_moe_max_tiles(n_slots, n_exp) + 1;
+    return (size_t)(n_exp + 1) + 3 * (size_t)n_slots + 2 * (size_t)ggb_moe_max_tiles(n_slots, n_exp) + 1;
 }
 
 static ggb_moe_groups groups_of(int32_t *ws, int64_t n, int n_exp, bool gather) {
@@ -143,8 +176,8 @@ int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t 
     const int64_t n = T * top;
     GGB_CHECK_ARG(idx && ws && T > 0 && top > 0 && n_exp > 0 && n_exp <= 8192 && n < (1ll << 30), "moe_group: bad arguments");
     const int mt = ggb_moe_max_tiles(n, n_exp);
-    int32_t *offsets = ws, *row_src = ws + n_exp + 1, *inv = row_src + n, *te = inv + n, *tr = te + mt, *nt = tr + mt;
-    moe_group_kernel<<<1, 1024, (size_t)n_exp * 4, ggb_cuda_stream()>>>(idx, (int)n, top, n_exp, offsets, row_src, inv, te, tr, nt);
+    int32_t *offsets = ws, *row_src = ws + n_exp + 1, *inv = row_src + n, *te = inv + n, *tr = te + mt, *nt = tr + mt, *re = nt + 1;
+    moe_group_kernel<<<1, 1024, (size_t)n_exp * 4, ggb_cuda_stream()>>>(idx, (int)n, top, n_exp, offsets, row_src, inv, te, tr, nt, re);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }
@@ -155,6 +188,19 @@ int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(w && a && ws && c && N > 0 && K > 0 && T > 0 && lda >= K && ldc >= N, "moe_linear: bad arguments");
     const ggb_moe_groups g = groups_of(const_cast<int32_t *>(ws), T * top, n_exp, gather != 0);
+    if (T * top <= 16) { // decode: every slot is a mat-vec on its expert's matrix
+        const int es = dt == GGB_TYPE_BF16 ? 2 : 4;
+        const int vec = K % (16 / es) == 0 && lda % (16 / es) == 0 && ((uintptr_t)w | (uintptr_t)a) % 16 == 0;
+        const int32_t *row_expert = g.n_tiles + 1;
+        const dim3 grid((unsigned)((N + 7) / 8), (unsigned)(T * top));
+#define MV(E)                                                                                                                         \
+    if (act) moe_vec_kernel<E, 1><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, nullptr, (E *)c, ldc, vec); \
+    else moe_vec_kernel<E, 0><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, (float *)c, nullptr, ldc, vec);
+        if (dt == GGB_TYPE_BF16) { MV(__nv_bfloat16) } else { MV(float) }
+#undef MV
+        GGB_LAUNCH_CHECK();
+        return GGB_OK;
+    }
     return ggb_linear_grouped_launch(dt, w, N, K, a, lda, ggb_moe_max_tiles(T * top, n_exp), act ? nullptr : (float *)c, act ? c : nullptr,
                                      ldc, act, g);
 }

@@ -107,6 +107,7 @@ class gemma_model {
     // Tolerance-exact (bf16 activations), unlike the token-by-token PREFILL above which is bit-exact.
     int prefill(const token_id *tokens, int T, int32_t pos0, token_id *next);
     int get_prefill_logits(int row, float *host) const; // row in [0, T) of the last prefill
+    const float *prefill_logits_dev() const { return pf_logits_; } // fp32 [T][n_vocab] of the last prefill, on the device
     double last_prefill_gemm_flops() const { return pf_flops_; }
 
     // one decode step through host buffers: H2D (token,pos), graph, D2H next token

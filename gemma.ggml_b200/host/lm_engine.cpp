@@ -7,6 +7,7 @@
 
 int lm_engine::init(lm_model *model, int64_t max_tokens, int page_size, int max_seqs) {
     model_.reset(model);
+    if (model->max_live_sequences() > 0) max_seqs = std::min(max_seqs, model->max_live_sequences());
     int rc = cache_.init(model->dtype(), model->cache_row_elems(), max_tokens, page_size, max_seqs);
     if (rc) {
         err_ = cache_.error();

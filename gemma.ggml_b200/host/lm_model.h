@@ -30,6 +30,7 @@ class lm_model {
     virtual std::vector<int64_t> cache_row_elems() const = 0;
     // called once, before the first forward: the cache the model reads and writes, and the longest sequence it will see
     virtual int bind_cache(paged_cache *cache, int64_t max_positions) = 0;
+    virtual int max_live_sequences() const { return 0; } // 0: as many as the engine has slots
     virtual int max_portion() const = 0; // most tokens one forward call takes; the engine cuts longer portions
     // runs the portion from the state earlier portions left in the cache; the logits of rows want[0 .. n_want) of the
     // portion stay on the device: logits_dev() = fp32 [n_want][vocab]

@@ -44,7 +44,8 @@ def from_dt(dt, buf, shape):
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
-@pytest.mark.parametrize("T,N,K", [(1, 37, 50), (2, 64, 128), (8, 33, 72), (9, 70, 45), (130, 96, 64), (64, 65, 200), (5, 3, 7)])
+@pytest.mark.parametrize("T,N,K", [(1, 37, 50), (2, 64, 128), (8, 33, 72), (9, 70, 45), (130, 96, 64), (64, 65, 200), (5, 3, 7),
+                                   (300, 544, 192), (64, 32, 64), (257, 1024, 512), (1100, 96, 1024)])
 def test_linear_any_shape(gpu, dt, T, N, K):
     r = np.random.default_rng(T * 1000 + N)
     wv, wu = as_dt(dt, r.standard_normal((N, K)))
@@ -199,7 +200,7 @@ def test_latent_attention_sink_takes_the_weight(gpu, dt):
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
-@pytest.mark.parametrize("T,E,top,Fe,W", [(1, 5, 2, 24, 40), (37, 12, 3, 20, 33), (200, 4, 1, 70, 48), (9, 3, 3, 8, 16)])
+@pytest.mark.parametrize("T,E,top,Fe,W", [(1, 5, 2, 24, 40), (37, 12, 3, 20, 33), (200, 4, 1, 70, 48), (9, 3, 3, 8, 16), (4, 6, 3, 16, 32), (2, 7, 2, 9, 13)])
 def test_mixture_of_experts(gpu, dt, T, E, top, Fe, W):
     r = np.random.default_rng(T + E)
     L = gpu.cuda_lib()
