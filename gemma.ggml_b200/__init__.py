@@ -140,7 +140,7 @@ _CUDA_SIG = {
     "ggb_latent_attn_scratch_bytes": (sz, [i64, i32, i32, i32]),
     "ggb_op_latent_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, vp]),
     "ggb_op_latent_attn_out": (i32, [i32, vp, i32, vp, vp, i64, i32, i32, i32, vp]),
-    "ggb_op_moe_route": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp]),
+    "ggb_op_moe_route": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp, vp]),
     "ggb_moe_max_tiles": (i32, [i64, i32]), "ggb_moe_group_ints": (sz, [i64, i32]),
     "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),
     "ggb_op_moe_linear": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, vp, i32, vp, i64]),

@@ -55,14 +55,16 @@ __global__ void __launch_bounds__(128) latent_kv_store_kernel(const float *__res
 }
 
 // ---- qa[t][h] = [W_uk_h^T qn | rot(qr)] * scale.  q rows hold, head by head, D unrotated then Dr rotated numbers.
-// A CTA takes kAbsT tokens of one head so that the head's W_uk slice is read once for all of them.
+// A CTA takes kAbsT tokens of one head and 64 of the R outputs; its four groups of 64 threads each take a quarter of the
+// D terms (loads of a group are independent and in flight together) and the quarters are added in a fixed order.
 constexpr int kAbsT = 8;
 template <typename E>
 __global__ void __launch_bounds__(256) latent_q_absorb_kernel(const float *__restrict__ q, int64_t ldq, int64_t T, int H, int D, int Dr,
                                                               int dims, const float *__restrict__ cs, const int32_t *__restrict__ pos0,
                                                               const E *__restrict__ w_uk, int R, float scale, float *__restrict__ qa) {
-    extern __shared__ float qs[]; // [kAbsT][D]
-    const int h = blockIdx.y, tid = threadIdx.x;
+    extern __shared__ float qs[]; // [kAbsT][D], then [4][kAbsT][64] partial sums
+    float *ps = qs + kAbsT * D;
+    const int h = blockIdx.y, tid = threadIdx.x, rl = tid & 63, dg = tid >> 6;
     const int64_t t0 = (int64_t)blockIdx.x * kAbsT;
     const int nt = (int)min((int64_t)kAbsT, T - t0);
     for (int i = tid; i < kAbsT * D; i += 256) {
@@ -71,21 +73,33 @@ __global__ void __launch_bounds__(256) latent_q_absorb_kernel(const float *__res
     }
     __syncthreads();
     const int QK = R + Dr;
-    for (int r = tid; r < R; r += 256) {
+    const int r = blockIdx.z * 64 + rl;
+    {
         float acc[kAbsT];
 #pragma unroll
         for (int tt = 0; tt < kAbsT; tt++) acc[tt] = 0.f;
-        const E *wc = w_uk + (int64_t)h * D * R + r;
+        const int dq = (D + 3) / 4, d0 = dg * dq, d1 = min(D, d0 + dq);
+        if (r < R) {
+            const E *wc = w_uk + (int64_t)h * D * R + r;
 #pragma unroll 8
-        for (int dd = 0; dd < D; dd++) {
-            const float w = to_f32(wc[(int64_t)dd * R]);
+            for (int dd = d0; dd < d1; dd++) {
+                const float w = to_f32(wc[(int64_t)dd * R]);
 #pragma unroll
-            for (int tt = 0; tt < kAbsT; tt++) acc[tt] = fmaf(qs[tt * D + dd], w, acc[tt]);
+                for (int tt = 0; tt < kAbsT; tt++) acc[tt] = fmaf(qs[tt * D + dd], w, acc[tt]);
+            }
         }
 #pragma unroll
-        for (int tt = 0; tt < kAbsT; tt++)
-            if (tt < nt) qa[((t0 + tt) * H + h) * QK + r] = acc[tt] * scale;
+        for (int tt = 0; tt < kAbsT; tt++) ps[(dg * kAbsT + tt) * 64 + rl] = acc[tt];
     }
+    __syncthreads();
+    for (int i = tid; i < nt * 64; i += 256) {
+        const int tt = i >> 6, l = i & 63, rr = blockIdx.z * 64 + l;
+        if (rr < R) {
+            const float v = ((ps[(0 * kAbsT + tt) * 64 + l] + ps[(1 * kAbsT + tt) * 64 + l]) + ps[(2 * kAbsT + tt) * 64 + l]) + ps[(3 * kAbsT + tt) * 64 + l];
+            qa[((t0 + tt) * H + h) * QK + rr] = v * scale;
+        }
+    }
+    if (blockIdx.z != 0) return;
     const int half = Dr / 2 + (Dr & 1);
     for (int i = tid; i < nt * half; i += 256) {
         const int tt = i / half, pi = i - tt * half;
@@ -94,9 +108,9 @@ __global__ void __launch_bounds__(256) latent_q_absorb_kernel(const float *__res
         float *dst = qa + (t * H + h) * QK + R;
         const int i0 = 2 * pi, i1 = i0 + 1;
         if (i1 < dims) {
-            const float u = src[i0], v = src[i1], c = cs[p * dims + 2 * pi], s = cs[p * dims + 2 * pi + 1];
-            dst[i0] = (u * c - v * s) * scale;
-            dst[i1] = (v * c + u * s) * scale;
+            const float u = src[i0], v = src[i1], c = cs[p * dims + 2 * pi], sn = cs[p * dims + 2 * pi + 1];
+            dst[i0] = (u * c - v * sn) * scale;
+            dst[i1] = (v * c + u * sn) * scale;
         } else {
             dst[i0] = src[i0] * scale;
             if (i1 < Dr) dst[i1] = src[i1] * scale;
@@ -112,6 +126,14 @@ template <typename E> struct TileWord;
 template <> struct TileWord<float> {
     static constexpr int per = 1;
     static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) { return fmaf(__uint_as_float(w), q[0], acc); }
+    // four words against q[0 .. 4)
+    static __device__ __forceinline__ void dot4(const uint32_t *w, const float *q, float (&a)[4]) {
+        const float4 q0 = *reinterpret_cast<const float4 *>(q);
+        a[0] = fmaf(__uint_as_float(w[0]), q0.x, a[0]);
+        a[1] = fmaf(__uint_as_float(w[1]), q0.y, a[1]);
+        a[2] = fmaf(__uint_as_float(w[2]), q0.z, a[2]);
+        a[3] = fmaf(__uint_as_float(w[3]), q0.w, a[3]);
+    }
 };
 template <> struct TileWord<__nv_bfloat16> {
     static constexpr int per = 2;
@@ -119,17 +141,30 @@ template <> struct TileWord<__nv_bfloat16> {
         acc = fmaf(__uint_as_float(w << 16), q[0], acc);
         return fmaf(__uint_as_float(w & 0xffff0000u), q[1], acc);
     }
+    // four words (eight numbers) against q[0 .. 8)
+    static __device__ __forceinline__ void dot4(const uint32_t *w, const float *q, float (&a)[4]) {
+        const float4 q0 = *reinterpret_cast<const float4 *>(q), q1 = *reinterpret_cast<const float4 *>(q + 4);
+        a[0] = fmaf(__uint_as_float(w[0] << 16), q0.x, a[0]);
+        a[1] = fmaf(__uint_as_float(w[0] & 0xffff0000u), q0.y, a[1]);
+        a[2] = fmaf(__uint_as_float(w[1] << 16), q0.z, a[2]);
+        a[3] = fmaf(__uint_as_float(w[1] & 0xffff0000u), q0.w, a[3]);
+        a[0] = fmaf(__uint_as_float(w[2] << 16), q1.x, a[0]);
+        a[1] = fmaf(__uint_as_float(w[2] & 0xffff0000u), q1.y, a[1]);
+        a[2] = fmaf(__uint_as_float(w[3] << 16), q1.z, a[2]);
+        a[3] = fmaf(__uint_as_float(w[3] & 0xffff0000u), q1.w, a[3]);
+    }
 };
 
 template <typename E, int RC>
 __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *__restrict__ qa, const E *__restrict__ cache, int64_t ldk,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
                                                                   int H, int R, int Dr, int n_split, int SW, float *__restrict__ part) {
-    extern __shared__ uint32_t la_smem[];
+    extern __shared__ __align__(16) uint32_t la_smem[];
     constexpr int PER = TileWord<E>::per;
-    const int QK = R + Dr, words = (QK + PER - 1) / PER, QKp = words * PER;
+    const int QK = R + Dr, words = (QK + PER - 1) / PER;
+    const int QKp = (words + 3) / 4 * 4 * PER; // q rows padded with zeros to whole groups of four words, 16-byte aligned
     uint32_t *tile = la_smem;                                     // [32][SW]
-    float *qsm = reinterpret_cast<float *>(la_smem + 32 * SW);    // [NW][QKp]
+    float *qsm = reinterpret_cast<float *>(la_smem + 32 * SW);     // [NW][QKp]; 32 * SW words = 128 * SW bytes: 16-byte aligned
     const int NW = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x, split = blockIdx.y;
     const int64_t n_kv = (int64_t)*pos0 + t + 1; // causal: the token sees itself and everything before
@@ -167,14 +202,15 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
             float s = -INFINITY;
             if (lane < rows) {
                 const uint32_t *tr = tile + lane * SW;
-                float a0 = 0.f, a1 = 0.f;
+                float a4[4] = {0.f, 0.f, 0.f, 0.f};
                 int w = 0;
-                for (; w + 1 < words; w += 2) {
-                    a0 = TileWord<E>::dot(tr[w], qh + w * PER, a0);
-                    a1 = TileWord<E>::dot(tr[w + 1], qh + (w + 1) * PER, a1);
+#pragma unroll 2
+                for (; w + 3 < words; w += 4) {
+                    const uint32_t tw[4] = {tr[w], tr[w + 1], tr[w + 2], tr[w + 3]};
+                    TileWord<E>::dot4(tw, qh + w * PER, a4);
                 }
-                if (w < words) a0 = TileWord<E>::dot(tr[w], qh + w * PER, a0);
-                s = a0 + a1;
+                for (; w < words; w++) a4[0] = TileWord<E>::dot(tr[w], qh + w * PER, a4[0]);
+                s = (a4[0] + a4[1]) + (a4[2] + a4[3]);
             }
             const float m_new = fmaxf(m, warp_max_f32(s));
             const float corr = expf(m - m_new), p = expf(s - m_new); // exp(-inf) = 0: first tile, rows past the end
@@ -204,11 +240,11 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
 }
 
 // ---- merge the splits with the sink, then out[t][h] = W_uv_h (sum_j p_j c_j).  kOutT tokens of one head per CTA.
-constexpr int kOutT = 8;
+constexpr int kOutT = 8; // tokens of one head per CTA; v_chunk outputs per CTA (every CTA of a head repeats the merge)
 template <typename E>
 __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__restrict__ part, int n_split, const float *__restrict__ sink,
                                                               const E *__restrict__ w_uv, int64_t T, int H, int R, int Dv,
-                                                              E *__restrict__ out) {
+                                                              int v_chunk, E *__restrict__ out) {
     extern __shared__ float ol[]; // [kOutT][R]
     const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t t0 = (int64_t)blockIdx.x * kOutT;
@@ -242,7 +278,8 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
         }
     }
     __syncthreads();
-    for (int v = warp; v < Dv; v += 8) {
+    const int v_end = min(Dv, ((int)blockIdx.z + 1) * v_chunk);
+    for (int v = blockIdx.z * v_chunk + warp; v < v_end; v += 8) {
         const E *wr = w_uv + ((int64_t)h * Dv + v) * R;
         float acc[kOutT];
 #pragma unroll
@@ -267,7 +304,7 @@ int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const i
     constexpr int PER = TileWord<E>::per;
     const int words = (R + Dr + PER - 1) / PER, SW = words | 1; // odd row pitch: lanes of a warp hit 32 different banks
     const int NW = H < 16 ? H : 16;
-    const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * words * PER * 4;
+    const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * ((words + 3) / 4 * 4) * PER * 4;
     GGB_CHECK_ARG(smem <= 200 * 1024, "latent_attn: rows of %d numbers do not fit shared memory", R + Dr);
     const dim3 grid((unsigned)T, (unsigned)n_split);
 #define LA_CASE(RC)                                                                                                          \
@@ -318,8 +355,8 @@ int ggb_op_latent_q_absorb(int dt, const float *q, int64_t ldq, int64_t T, int H
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(q && cos_sin && pos0 && w_uk && qa && T > 0 && H > 0 && D > 0 && R > 0 && rot_dims <= Dr && rot_dims % 2 == 0,
                   "latent_q_absorb: bad arguments");
-    const dim3 grid((unsigned)((T + kAbsT - 1) / kAbsT), (unsigned)H);
-    const size_t smem = (size_t)kAbsT * D * 4;
+    const dim3 grid((unsigned)((T + kAbsT - 1) / kAbsT), (unsigned)H, (unsigned)((R + 63) / 64));
+    const size_t smem = (size_t)kAbsT * D * 4 + (size_t)4 * kAbsT * 64 * 4;
     GGB_CHECK_ARG(smem <= 48 * 1024, "latent_q_absorb: head dimension %d too large", D);
     if (dt == GGB_TYPE_BF16)
         latent_q_absorb_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(q, ldq, T, H, D, Dr, rot_dims, cos_sin, pos0,
@@ -353,14 +390,16 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(part && sink && w_uv && out && T > 0 && H > 0 && R > 0 && Dv > 0 && n_split > 0, "latent_attn_out: bad arguments");
-    const dim3 grid((unsigned)((T + kOutT - 1) / kOutT), (unsigned)H);
+    // few tokens: spread a head's outputs over several CTAs; many tokens: the grid is large already, merge once per head
+    const int v_chunk = T * H >= 1024 ? Dv : 16;
+    const dim3 grid((unsigned)((T + kOutT - 1) / kOutT), (unsigned)H, (unsigned)((Dv + v_chunk - 1) / v_chunk));
     const size_t smem = (size_t)kOutT * (R + n_split) * 4;
     GGB_CHECK_ARG(smem <= 48 * 1024, "latent_attn_out: latent size %d with %d splits too large", R, n_split);
     if (dt == GGB_TYPE_BF16)
         latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const __nv_bfloat16 *)w_uv, T, H, R, Dv,
-                                                                       (__nv_bfloat16 *)out);
+                                                                       v_chunk, (__nv_bfloat16 *)out);
     else
-        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const float *)w_uv, T, H, R, Dv, (float *)out);
+        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const float *)w_uv, T, H, R, Dv, v_chunk, (float *)out);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

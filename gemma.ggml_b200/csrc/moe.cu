@@ -10,25 +10,43 @@
 
 namespace {
 
-// one CTA (4 warps) per token: z[e] = w[e] . h + b[e]; then `top` rounds of arg-max (ties: the lower index)
+// router logits: a warp per (token, expert), z[t][e] = w[e] . h[t] + b[e] in fp32
 template <typename E>
-__global__ void __launch_bounds__(128) moe_route_kernel(const E *__restrict__ h, int64_t W, const float *__restrict__ w,
-                                                        const float *__restrict__ b, int n_exp, int top, int32_t *__restrict__ idx,
+__global__ void __launch_bounds__(256) moe_logits_kernel(const E *__restrict__ h, int64_t W, int64_t T, const float *__restrict__ w,
+                                                         const float *__restrict__ b, int n_exp, float *__restrict__ z) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= T * n_exp) return;
+    const int64_t t = i / n_exp;
+    const int e = (int)(i - t * n_exp);
+    const E *hr = h + t * W;
+    const float *wr = w + (int64_t)e * W;
+    float s = 0.f;
+    if (W % 4 == 0) {
+#pragma unroll 4
+        for (int64_t k = (int64_t)lane * 4; k < W; k += 128) {
+            const float4 wv = *reinterpret_cast<const float4 *>(wr + k);
+            s = fmaf(wv.x, to_f32(hr[k]), s);
+            s = fmaf(wv.y, to_f32(hr[k + 1]), s);
+            s = fmaf(wv.z, to_f32(hr[k + 2]), s);
+            s = fmaf(wv.w, to_f32(hr[k + 3]), s);
+        }
+    } else {
+        for (int64_t k = lane; k < W; k += 32) s = fmaf(wr[k], to_f32(hr[k]), s);
+    }
+    s = warp_sum_f32(s);
+    if (lane == 0) z[i] = s + (b ? b[e] : 0.f);
+}
+
+// one warp per token: `top` rounds of arg-max over its logits (ties: the lower index), soft-max over the chosen
+__global__ void __launch_bounds__(32) moe_select_kernel(const float *__restrict__ zg, int n_exp, int top, int32_t *__restrict__ idx,
                                                         float *__restrict__ wt) {
     extern __shared__ float z[]; // [n_exp] logits, then [top] chosen values
     float *sel = z + n_exp;
     const int64_t t = blockIdx.x;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const E *hr = h + t * W;
-    for (int e = warp; e < n_exp; e += 4) {
-        float s = 0.f;
-#pragma unroll 8
-        for (int64_t k = lane; k < W; k += 32) s = fmaf(w[(int64_t)e * W + k], to_f32(hr[k]), s);
-        s = warp_sum_f32(s);
-        if (lane == 0) z[e] = s + (b ? b[e] : 0.f);
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    const int lane = threadIdx.x;
+    for (int e = lane; e < n_exp; e += 32) z[e] = zg[t * n_exp + e];
+    __syncwarp();
     for (int k = 0; k < top; k++) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
@@ -141,16 +159,20 @@ extern "C" {
 #define GGB_CHECK_DT(dt) GGB_CHECK_ARG((dt) == GGB_TYPE_BF16 || (dt) == GGB_TYPE_F32, "dtype %d is neither bf16 nor f32", (int)(dt))
 
 int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *bias, int n_exp, int top,
-                     int32_t *idx, float *wt) {
+                     float *logits, int32_t *idx, float *wt) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(h && w_router && idx && wt && W > 0 && T > 0 && n_exp > 0 && top > 0 && top <= n_exp && n_exp <= 8192,
                   "moe_route: bad arguments");
+    GGB_CHECK_ARG(logits != nullptr, "moe_route: needs T * n_exp floats for the logits");
     const size_t smem = (size_t)(n_exp + top) * 4;
+    const unsigned blocks = (unsigned)((T * n_exp + 7) / 8);
     if (dt == GGB_TYPE_BF16)
-        moe_route_kernel<<<(unsigned)T, 128, smem, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, w_router, bias, n_exp, top, idx, wt);
+        moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, T, w_router, bias, n_exp, logits);
     else
-        moe_route_kernel<<<(unsigned)T, 128, smem, ggb_cuda_stream()>>>((const float *)h, W, w_router, bias, n_exp, top, idx, wt);
+        moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const float *)h, W, T, w_router, bias, n_exp, logits);
+    GGB_LAUNCH_CHECK();
+    moe_select_kernel<<<(unsigned)T, 32, smem, ggb_cuda_stream()>>>(logits, n_exp, top, idx, wt);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

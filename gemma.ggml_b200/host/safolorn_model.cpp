@@ -398,7 +398,7 @@ std::vector<int64_t> safolorn_model::cache_row_elems() const {
 int safolorn_model::alloc_scratch() {
     const sf_config &c = cfg_;
     const int64_t T = max_T_, W = c.width;
-    int64_t nqd = 0, hqk = 0, hr = 0, hdv = 0, ff2 = 0, ffd = 0, slots = 0, effe = 0, ints = 0, top = 0;
+    int64_t nqd = 0, hqk = 0, hr = 0, hdv = 0, ff2 = 0, ffd = 0, slots = 0, effe = 0, ints = 0, top = 0, n_exp_max = 0;
     for (const sf_layer_cfg &l : c.layers) {
         const int64_t nq = (int64_t)l.heads * (l.dim + l.rot_dim) + (l.kv_from < 0 ? l.kv_rank + l.rot_dim : 0);
         nqd = std::max(nqd, nq);
@@ -411,6 +411,7 @@ int safolorn_model::alloc_scratch() {
             effe = std::max(effe, T * l.top * l.ff);
             ints = std::max(ints, (int64_t)ggb_moe_group_ints(T * l.top, l.experts));
             top = std::max(top, (int64_t)l.top);
+            n_exp_max = std::max(n_exp_max, (int64_t)l.experts);
         }
     }
     part_rows_ = std::max<int64_t>(T, 320);
@@ -437,6 +438,7 @@ int safolorn_model::alloc_scratch() {
     SF_ALLOC(act_, T * ffd * es);
     SF_ALLOC(route_i_, T * top * 4);
     SF_ALLOC(route_w_, T * top * 4);
+    SF_ALLOC(route_z_, T * n_exp_max * 4);
     SF_ALLOC(group_ws_, ints * 4);
     SF_ALLOC(y1_, effe * es);
     SF_ALLOC(y2_, slots * W * 4);
@@ -491,7 +493,7 @@ int safolorn_model::emit(int T, int ns, const int32_t *table, int n_want) {
             SF_OP("op_act", ggb_op_glu_clamp(dt_, gu_, l.ff, t, l.limit, 1.702f, act_));
             SF_OP("op_linear", ggb_op_linear(dt_, w.down, W, l.ff, act_, l.ff, t, ff_o_, W));
         } else if (l.mlp == 2) {
-            SF_OP("op_moe", ggb_op_moe_route(dt_, h2_, W, t, w.router, w.router_b, l.experts, l.top, route_i_, route_w_));
+            SF_OP("op_moe", ggb_op_moe_route(dt_, h2_, W, t, w.router, w.router_b, l.experts, l.top, route_z_, route_i_, route_w_));
             SF_OP("op_moe", ggb_op_moe_group(route_i_, t, l.top, l.experts, group_ws_));
             SF_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_up, l.ff, W, h2_, W, 1, t, l.top, l.experts, group_ws_, 1, y1_, l.ff));
             SF_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_down, W, l.ff, y1_, l.ff, 0, t, l.top, l.experts, group_ws_, 0, y2_, W));
@@ -526,7 +528,7 @@ int safolorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
     if (n_want) SF_TRY(ggb_upload(want_, want, (size_t)n_want * 4));
     // splits of the visible positions: enough CTAs for a short portion, one split once the tokens fill the GPU
     const int64_t n_kv = p.pos0 + p.T;
-    int64_t ns = std::min<int64_t>((n_kv + 127) / 128, std::max<int64_t>(1, 296 / p.T));
+    int64_t ns = std::min<int64_t>((n_kv + (p.T == 1 ? 31 : 127)) / (p.T == 1 ? 32 : 128), std::max<int64_t>(1, 296 / p.T));
     ns = std::max<int64_t>(1, std::min<int64_t>(ns, 64));
     if (p.T == 1) { // powers of two: the captured one-token step changes rarely
         int64_t q = 1;

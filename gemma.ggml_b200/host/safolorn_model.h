@@ -113,7 +113,7 @@ class safolorn_model : public lm_model {
     // activations (sized for max_T_ tokens and the widest layer)
     float *x_ = nullptr, *qd_ = nullptr, *qa_ = nullptr, *part_ = nullptr, *attn_o_ = nullptr, *gu_ = nullptr, *ff_o_ = nullptr;
     void *h1_ = nullptr, *h2_ = nullptr, *ao_ = nullptr, *act_ = nullptr, *y1_ = nullptr, *hw_ = nullptr;
-    float *y2_ = nullptr, *route_w_ = nullptr, *xw_ = nullptr, *logits_ = nullptr, *cap_ = nullptr;
+    float *y2_ = nullptr, *route_w_ = nullptr, *route_z_ = nullptr, *xw_ = nullptr, *logits_ = nullptr, *cap_ = nullptr;
     int32_t *route_i_ = nullptr, *group_ws_ = nullptr;
     int64_t part_rows_ = 0;
     bool capture_ = false;

@@ -300,7 +300,7 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
  * c[sorted row] = a[row] w_e^T with w = [n_exp][N][K]; gather: a is indexed by token (first product), else by sorted
  * row; act 1: c = relu(.)^2 in dt, act 0: c fp32.  combine: out[t] = sum_s wt[t][s] y[sorted row of slot s]. */
 int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *bias, int n_exp, int top,
-                     int32_t *idx, float *wt);
+                     float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt);
 int ggb_moe_max_tiles(int64_t n_slots, int n_exp);
 size_t ggb_moe_group_ints(int64_t n_slots, int n_exp);
 int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t *ws);

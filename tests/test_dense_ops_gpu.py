@@ -218,7 +218,8 @@ def test_mixture_of_experts(gpu, dt, T, E, top, Fe, W):
     es = 2 if dt == BF16 else 4
     y1, y2, out = gpu.DeviceBuffer(T * top * Fe * es), gpu.DeviceBuffer(T * top * W * 4), gpu.DeviceBuffer(T * W * 4)
     hb = dev(gpu, hu)
-    gpu.check(L.ggb_op_moe_route(dt, hb.ptr, W, T, dev(gpu, wr).ptr, dev(gpu, b).ptr, E, top, idx.ptr, wt.ptr), "route")
+    zb = gpu.DeviceBuffer(T * E * 4)
+    gpu.check(L.ggb_op_moe_route(dt, hb.ptr, W, T, dev(gpu, wr).ptr, dev(gpu, b).ptr, E, top, zb.ptr, idx.ptr, wt.ptr), "route")
     gpu.check(L.ggb_op_moe_group(idx.ptr, T, top, E, ws.ptr), "group")
     gpu.check(L.ggb_op_moe_linear(dt, dev(gpu, upu).ptr, Fe, W, hb.ptr, W, 1, T, top, E, ws.ptr, 1, y1.ptr, Fe), "up")
     gpu.check(L.ggb_op_moe_linear(dt, dev(gpu, dnu).ptr, W, Fe, y1.ptr, Fe, 0, T, top, E, ws.ptr, 0, y2.ptr, W), "down")
