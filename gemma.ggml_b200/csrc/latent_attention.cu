@@ -126,6 +126,13 @@ template <typename E> struct TileWord;
 template <> struct TileWord<float> {
     static constexpr int per = 1;
     static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) { return fmaf(__uint_as_float(w), q[0], acc); }
+    // accumulator i of a lane holds coordinate coord(lane, i) of sum_j p_j c_j
+    static __device__ __forceinline__ int coord(int lane, int i) { return lane + 32 * i; }
+    template <int RC> static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, float pj, float (&acc)[RC]) {
+#pragma unroll
+        for (int i = 0; i < RC; i++)
+            if (lane + 32 * i < R) acc[i] = fmaf(pj, __uint_as_float(row[lane + 32 * i]), acc[i]);
+    }
     // four words against q[0 .. 4)
     static __device__ __forceinline__ void dot4(const uint32_t *w, const float *q, float (&a)[4]) {
         const float4 q0 = *reinterpret_cast<const float4 *>(q);
@@ -140,6 +147,19 @@ template <> struct TileWord<__nv_bfloat16> {
     static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) {
         acc = fmaf(__uint_as_float(w << 16), q[0], acc);
         return fmaf(__uint_as_float(w & 0xffff0000u), q[1], acc);
+    }
+    // a lane owns the two numbers of word lane + 32 k: accumulators 2k and 2k + 1 (one 32-bit read for both)
+    static __device__ __forceinline__ int coord(int lane, int i) { return 2 * (lane + 32 * (i >> 1)) + (i & 1); }
+    template <int RC> static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, float pj, float (&acc)[RC]) {
+#pragma unroll
+        for (int k = 0; k < RC / 2; k++) {
+            const int w = lane + 32 * k;
+            if (2 * w < R) { // R odd: the upper half of the last word is the first number of kr; its accumulator is not stored
+                const uint32_t v = row[w];
+                acc[2 * k] = fmaf(pj, __uint_as_float(v << 16), acc[2 * k]);
+                acc[2 * k + 1] = fmaf(pj, __uint_as_float(v & 0xffff0000u), acc[2 * k + 1]);
+            }
+        }
     }
     // four words (eight numbers) against q[0 .. 8)
     static __device__ __forceinline__ void dot4(const uint32_t *w, const float *q, float (&a)[4]) {
@@ -158,8 +178,9 @@ template <> struct TileWord<__nv_bfloat16> {
 template <typename E, int RC>
 __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *__restrict__ qa, const E *__restrict__ cache, int64_t ldk,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
-                                                                  int H, int R, int Dr, int n_split, int SW, float *__restrict__ part) {
+                                                                  int H, int R, int Dr, int n_split, int SW, int hpc, float *__restrict__ part) {
     extern __shared__ __align__(16) uint32_t la_smem[];
+    __shared__ int64_t rowoff[32];
     constexpr int PER = TileWord<E>::per;
     const int QK = R + Dr, words = (QK + PER - 1) / PER;
     const int QKp = (words + 3) / 4 * 4 * PER; // q rows padded with zeros to whole groups of four words, 16-byte aligned
@@ -168,12 +189,12 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
     const int NW = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x, split = blockIdx.y;
     const int64_t n_kv = (int64_t)*pos0 + t + 1; // causal: the token sees itself and everything before
-    int64_t chunk = (n_kv + n_split - 1) / n_split;
-    chunk = (chunk + 31) / 32 * 32;
-    const int64_t j0 = (int64_t)split * chunk, j1 = min(j0 + chunk, n_kv);
-    for (int h0 = 0; h0 < H; h0 += NW) {
+    // tiles of 32 positions are dealt to the splits in turn: split s takes tiles s, s + n_split, ...
+    const int64_t j0 = (int64_t)split * 32, j1 = n_kv, jstep = (int64_t)32 * n_split;
+    const int h_begin = blockIdx.z * hpc, h_end = min(H, h_begin + hpc);
+    for (int h0 = h_begin; h0 < h_end; h0 += NW) {
         const int h = h0 + warp;
-        const bool live = h < H;
+        const bool live = h < h_end;
         __syncthreads(); // the previous group's q and tile are no longer read
         for (int k = lane; k < QKp; k += 32) // every warp stages its own head
             qsm[warp * QKp + k] = (live && k < QK) ? qa[((int64_t)t * H + h) * QK + k] : 0.f;
@@ -181,20 +202,38 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
 #pragma unroll
         for (int i = 0; i < RC; i++) acc[i] = 0.f;
         const float *qh = qsm + warp * QKp;
-        for (int64_t j = j0; j < j1; j += 32) {
+        for (int64_t j = j0; j < j1; j += jstep) {
             __syncthreads();
             const int rows = (int)min((int64_t)32, j1 - j);
-            // a warp copies whole rows: one page lookup per row, then 16-byte loads that are all in flight together
-            // (cache rows start on 16-byte boundaries: their pitch is a multiple of 8 numbers)
-            for (int jj = warp; jj < rows; jj += NW) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(cache + cache_row(table, B, j + jj) * ldk);
-                uint32_t *dst = tile + jj * SW;
-                for (int w4 = lane; w4 * 4 < words; w4 += 32) {
-                    const uint4 v = src[w4];
-                    dst[w4 * 4] = v.x;
-                    if (w4 * 4 + 1 < words) dst[w4 * 4 + 1] = v.y;
-                    if (w4 * 4 + 2 < words) dst[w4 * 4 + 2] = v.z;
-                    if (w4 * 4 + 3 < words) dst[w4 * 4 + 3] = v.w;
+            // page lookups of the tile's rows side by side (one thread per row), then one flat sweep of 16-byte loads
+            // over all rows: nothing in it waits for anything else (cache rows start on 16-byte boundaries)
+            if (threadIdx.x < rows) rowoff[threadIdx.x] = cache_row(table, B, j + threadIdx.x) * ldk;
+            __syncthreads();
+            {
+                const int w4n = (words + 3) / 4, total = rows * w4n;
+                for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * 4) {
+                    uint4 v[4];
+                    int at[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int i = i0 + u * blockDim.x;
+                        at[u] = -1;
+                        if (i < total) {
+                            const int jj = i / w4n, w4 = i - jj * w4n;
+                            v[u] = reinterpret_cast<const uint4 *>(cache + rowoff[jj])[w4];
+                            at[u] = jj * SW + w4 * 4;
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        if (at[u] < 0) continue;
+                        const int w0 = (at[u] % SW);
+                        uint32_t *dst = tile + at[u];
+                        dst[0] = v[u].x;
+                        if (w0 + 1 < words) dst[1] = v[u].y;
+                        if (w0 + 2 < words) dst[2] = v[u].z;
+                        if (w0 + 3 < words) dst[3] = v[u].w;
+                    }
                 }
             }
             __syncthreads();
@@ -220,10 +259,7 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
             for (int i = 0; i < RC; i++) acc[i] *= corr;
             for (int jj = 0; jj < rows; jj++) {
                 const float pj = __shfl_sync(0xffffffffu, p, jj);
-                const E *cr = reinterpret_cast<const E *>(tile + jj * SW);
-#pragma unroll
-                for (int i = 0; i < RC; i++)
-                    if (lane + 32 * i < R) acc[i] = fmaf(pj, to_f32(cr[lane + 32 * i]), acc[i]);
+                TileWord<E>::template pv<RC>(tile + jj * SW, lane, R, pj, acc);
             }
         }
         if (live) {
@@ -233,8 +269,10 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
                 o[1] = l;
             }
 #pragma unroll
-            for (int i = 0; i < RC; i++)
-                if (lane + 32 * i < R) o[2 + lane + 32 * i] = acc[i];
+            for (int i = 0; i < RC; i++) {
+                const int r = TileWord<E>::coord(lane, i);
+                if (r < R) o[2 + r] = acc[i];
+            }
         }
     }
 }
@@ -272,7 +310,7 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
         const float *p0 = part + (((t0 + tt) * n_split) * H + h) * (R + 2) + 2;
         for (int r = tid; r < R; r += 256) {
             float a = 0.f;
-#pragma unroll 8
+#pragma unroll 16
             for (int s = 0; s < n_split; s++) a = fmaf(p0[s * ps + r], wsm[tt * n_split + s], a);
             ol[tt * R + r] = a;
         }
@@ -284,11 +322,26 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
         float acc[kOutT];
 #pragma unroll
         for (int tt = 0; tt < kOutT; tt++) acc[tt] = 0.f;
+        constexpr int VE = 16 / (int)sizeof(E);
+        if (R % VE == 0 && (reinterpret_cast<uintptr_t>(w_uv) & 15) == 0) {
 #pragma unroll 4
-        for (int k = lane; k < R; k += 32) {
-            const float w = to_f32(wr[k]);
+            for (int k = lane * VE; k < R; k += 32 * VE) {
+                const uint4 wv = *reinterpret_cast<const uint4 *>(wr + k);
+                const E *we = reinterpret_cast<const E *>(&wv);
 #pragma unroll
-            for (int tt = 0; tt < kOutT; tt++) acc[tt] = fmaf(w, ol[tt * R + k], acc[tt]);
+                for (int u = 0; u < VE; u++) {
+                    const float w = to_f32(we[u]);
+#pragma unroll
+                    for (int tt = 0; tt < kOutT; tt++) acc[tt] = fmaf(w, ol[tt * R + k + u], acc[tt]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = lane; k < R; k += 32) {
+                const float w = to_f32(wr[k]);
+#pragma unroll
+                for (int tt = 0; tt < kOutT; tt++) acc[tt] = fmaf(w, ol[tt * R + k], acc[tt]);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < kOutT; tt++) {
@@ -303,15 +356,18 @@ int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const i
                         int R, int Dr, int n_split, float *part) {
     constexpr int PER = TileWord<E>::per;
     const int words = (R + Dr + PER - 1) / PER, SW = words | 1; // odd row pitch: lanes of a warp hit 32 different banks
-    const int NW = H < 16 ? H : 16;
+    // heads per CTA: all of them (one warp each, up to 16 at a time) when many tokens share the GPU, groups of 4 when a
+    // handful of tokens must fill it (the tile is then staged once per group)
+    const int hpc = T >= 64 ? H : (H < 4 ? H : 4);
+    const int NW = hpc < 16 ? hpc : 16;
     const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * ((words + 3) / 4 * 4) * PER * 4;
     GGB_CHECK_ARG(smem <= 200 * 1024, "latent_attn: rows of %d numbers do not fit shared memory", R + Dr);
-    const dim3 grid((unsigned)T, (unsigned)n_split);
+    const dim3 grid((unsigned)T, (unsigned)n_split, (unsigned)((H + hpc - 1) / hpc));
 #define LA_CASE(RC)                                                                                                          \
     {                                                                                                                        \
         auto k = latent_attn_partial_kernel<E, RC>;                                                                          \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, H, R, Dr, n_split, SW, part); \
+        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, H, R, Dr, n_split, SW, hpc, part); \
     }
     if (R <= 64) LA_CASE(2)
     else if (R <= 128) LA_CASE(4)

@@ -528,7 +528,7 @@ int safolorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
     if (n_want) SF_TRY(ggb_upload(want_, want, (size_t)n_want * 4));
     // splits of the visible positions: enough CTAs for a short portion, one split once the tokens fill the GPU
     const int64_t n_kv = p.pos0 + p.T;
-    int64_t ns = std::min<int64_t>((n_kv + (p.T == 1 ? 31 : 127)) / (p.T == 1 ? 32 : 128), std::max<int64_t>(1, 296 / p.T));
+    int64_t ns = std::min<int64_t>((n_kv + (p.T <= 8 ? 31 : 127)) / (p.T <= 8 ? 32 : 128), std::max<int64_t>(1, 296 / p.T));
     ns = std::max<int64_t>(1, std::min<int64_t>(ns, 64));
     if (p.T == 1) { // powers of two: the captured one-token step changes rarely
         int64_t q = 1;
