@@ -23,6 +23,12 @@ int ggb_linear_grouped_launch(int dt, const void *w, int64_t N, int64_t K, const
 bool ggb_gemm_dense_bf16_fits(int64_t N, int64_t K, int64_t T, int64_t ldc);
 int ggb_gemm_dense_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t T, float *c, int64_t ldc);
 
+// the grouped tcgen05 form: w [n_exp][N][K] bf16, a rows in sorted-slot order, offsets [n_exp + 1] on the device;
+// c fp32 or (c_act) bf16 relu(c)^2
+bool ggb_gemm_grouped_bf16_fits(int64_t N, int64_t K, int64_t ldc);
+int ggb_gemm_grouped_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t n_rows, int n_exp, const int32_t *offsets, float *c,
+                          void *c_act, int64_t ldc);
+
 #ifdef __CUDACC__
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -283,7 +283,7 @@ template <typename E>
 __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__restrict__ part, int n_split, const float *__restrict__ sink,
                                                               const E *__restrict__ w_uv, int64_t T, int H, int R, int Dv,
                                                               int v_chunk, E *__restrict__ out) {
-    extern __shared__ float ol[]; // [kOutT][R]
+    extern __shared__ __align__(16) float ol[]; // [kOutT][R]
     const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t t0 = (int64_t)blockIdx.x * kOutT;
     const int nt = (int)min((int64_t)kOutT, T - t0);
@@ -328,11 +328,19 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
             for (int k = lane * VE; k < R; k += 32 * VE) {
                 const uint4 wv = *reinterpret_cast<const uint4 *>(wr + k);
                 const E *we = reinterpret_cast<const E *>(&wv);
+                float wf[VE];
 #pragma unroll
-                for (int u = 0; u < VE; u++) {
-                    const float w = to_f32(we[u]);
+                for (int u = 0; u < VE; u++) wf[u] = to_f32(we[u]);
 #pragma unroll
-                    for (int tt = 0; tt < kOutT; tt++) acc[tt] = fmaf(w, ol[tt * R + k + u], acc[tt]);
+                for (int tt = 0; tt < kOutT; tt++) { // the lane's VE numbers of a token as 16-byte shared-memory reads
+#pragma unroll
+                    for (int u = 0; u < VE; u += 4) {
+                        const float4 o4 = *reinterpret_cast<const float4 *>(ol + tt * R + k + u);
+                        acc[tt] = fmaf(wf[u], o4.x, acc[tt]);
+                        acc[tt] = fmaf(wf[u + 1], o4.y, acc[tt]);
+                        acc[tt] = fmaf(wf[u + 2], o4.z, acc[tt]);
+                        acc[tt] = fmaf(wf[u + 3], o4.w, acc[tt]);
+                    }
                 }
             }
         } else {

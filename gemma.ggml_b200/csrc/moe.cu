@@ -142,6 +142,12 @@ __global__ void __launch_bounds__(256) moe_vec_kernel(const E *__restrict__ w, i
     }
 }
 
+// rows of A in sorted-slot order (the tensor-core product reads its operand contiguously): y[i] = a[row_src[i]], 16 bytes a thread
+__global__ void moe_gather_kernel(const uint4 *__restrict__ a, int64_t row_u4, const int32_t *__restrict__ row_src, uint4 *__restrict__ y) {
+    const uint4 *src = a + (int64_t)row_src[blockIdx.x] * row_u4;
+    for (int64_t i = threadIdx.x; i < row_u4; i += blockDim.x) y[(int64_t)blockIdx.x * row_u4 + i] = src[i];
+}
+
 __global__ void moe_combine_kernel(const float *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ wt, int top,
                                    int64_t W, float *__restrict__ out) {
     const int64_t t = blockIdx.x;
@@ -222,6 +228,26 @@ int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a
 #undef MV
         GGB_LAUNCH_CHECK();
         return GGB_OK;
+    }
+    // many slots, bf16, aligned shapes: the tcgen05 GEMM, one launch over (N tiles, row tiles, experts)
+    if (dt == GGB_TYPE_BF16 && T * top >= 512 && ggb_gemm_grouped_bf16_fits(N, K, ldc) && lda == K && ((uintptr_t)a & 15) == 0) {
+        const int64_t n = T * top;
+        const void *a_sorted = a;
+        if (gather) {
+            static void *gbuf = nullptr;
+            static size_t gbytes = 0;
+            const size_t need = (size_t)n * (size_t)K * 2;
+            if (need > gbytes) {
+                if (gbuf) cudaFree(gbuf);
+                gbuf = nullptr, gbytes = 0;
+                GGB_CUDA(cudaMalloc(&gbuf, need));
+                gbytes = need;
+            }
+            moe_gather_kernel<<<(unsigned)n, 128, 0, ggb_cuda_stream()>>>((const uint4 *)a, K / 8, g.row_src, (uint4 *)gbuf);
+            GGB_LAUNCH_CHECK();
+            a_sorted = gbuf;
+        }
+        return ggb_gemm_grouped_bf16(w, N, K, a_sorted, n, n_exp, g.offsets, act ? nullptr : (float *)c, act ? c : nullptr, ldc);
     }
     return ggb_linear_grouped_launch(dt, w, N, K, a, lda, ggb_moe_max_tiles(T * top, n_exp), act ? nullptr : (float *)c, act ? c : nullptr,
                                      ldc, act, g);

@@ -108,6 +108,10 @@ struct GemmArgs {
     float *ws;         // K-split workspace [ksplit][T][N] or null (ksplit == 1: tiles go straight to seg.c)
     const float *resid; // [T][seg[0].ldc] or null (single segment, ksplit == 1)
     int kblocks_per_split; // 64-wide K blocks per split
+    // grouped form (mixture of experts, plain bf16 matrices): blockIdx.z = expert e, whose matrix is seg[0].qs + e * rows * K
+    // and whose rows of A / C are [m_ranges[e], m_ranges[e + 1]) (device int32); tiles past the range leave at once
+    const int32_t *m_ranges;
+    __nv_bfloat16 *act_out; // when set: C is stored as bf16 relu(c)^2 with row pitch seg[0].ldc instead of fp32
 };
 
 // int8 / int4 code -> fp32 without the conversion pipe: the (biased) code is dropped into the mantissa of
@@ -160,7 +164,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
     const uint32_t bars = smem0 + kStages * kStageBytes;                // full[kStages], empty[kStages], tmem_full
     const uint32_t tmem_slot = bars + 8 * (2 * kStages + 1);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, split = blockIdx.z;
+    int m_begin = 0, m_end = A.T, split = blockIdx.z;
+    size_t w_off = 0; // bytes from the segment's matrix to this CTA's matrix (grouped form)
+    if (A.m_ranges) {
+        m_begin = A.m_ranges[blockIdx.z];
+        m_end = A.m_ranges[blockIdx.z + 1];
+        split = 0;
+        w_off = (size_t)blockIdx.z * (size_t)A.seg[0].rows * (size_t)A.K * 2;
+    }
+    const int n0 = blockIdx.x * BN, m0 = m_begin + blockIdx.y * BM;
+    if (m0 >= m_end) return; // the whole CTA, before any barrier or tensor memory exists
     int si = 0;
     if (A.n_seg > 1 && n0 >= A.seg[1].n_begin) si = (A.n_seg > 2 && n0 >= A.seg[2].n_begin) ? 2 : 1;
     const GemmSeg &sg = A.seg[si];
@@ -231,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
                     for (int r = tid >> 3; r < BM; r += kProducerThreads / 8) {
                         const int row = m0 + r;
                         const uint32_t dst = sa + r * 128 + ((ch ^ (r & 7)) << 4);
-                        if (row < A.T) {
+                        if (row < m_end) {
                             const void *src = reinterpret_cast<const uint4 *>(A.a + (size_t)row * A.K + (size_t)kb * BK) + ch;
                             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
                         } else {
@@ -242,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
                 // W tile.  Plain bf16 matrix: the same copy as the A tile (rows of the matrix are K-major already)
                 if (TYPE == GGB_TYPE_BF16) {
                     const int ch = tid & 7;
-                    const __nv_bfloat16 *wm = reinterpret_cast<const __nv_bfloat16 *>(sg.qs);
+                    const __nv_bfloat16 *wm = reinterpret_cast<const __nv_bfloat16 *>(sg.qs + w_off);
 #pragma unroll
                     for (int r = tid >> 3; r < BN; r += kProducerThreads / 8) {
                         const int row = sn0 + r;
@@ -310,7 +323,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16w_kernel(const GemmA
             for (int c0 = chalf * (BN / 4); c0 < (chalf + 1) * (BN / 4); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(mt * BN + c0), v);
-                if (row < A.T && sn0 + c0 < sg.rows) { // rows % 32 == 0
+                if (row < m_end && sn0 + c0 < sg.rows && A.act_out) { // expert activation: relu(c)^2 as bf16
+                    __nv_bfloat16 *dst = A.act_out + (size_t)row * sg.ldc + sn0 + c0;
+#pragma unroll
+                    for (int u = 0; u < 32; u += 8) {
+                        __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            const float f = __uint_as_float(v[u + q]);
+                            o[q] = __float2bfloat16_rn(f > 0.f ? f * f : 0.f);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + u) = *reinterpret_cast<const uint4 *>(o);
+                    }
+                } else
+                if (row < m_end && sn0 + c0 < sg.rows) { // rows % 32 == 0
                     float *dst = cbase + (size_t)row * cld + c0;
                     const float *rs = A.resid ? A.resid + (size_t)row * sg.ldc + sn0 + c0 : nullptr;
 #pragma unroll
@@ -840,6 +866,31 @@ int ggb_op_attn_prefill(const float *q, const void *kcache, const void *vcache, 
 }
 
 } // extern "C"
+
+// The grouped form for a mixture of experts: w = [n_exp][N][K] bf16, a / c rows in sorted-slot order, offsets[e] .. offsets[e+1]
+// the rows of expert e (device).  One launch: grid (N tiles, row tiles of the longest possible group, experts).
+bool ggb_gemm_grouped_bf16_fits(int64_t N, int64_t K, int64_t ldc) { return K % 64 == 0 && N % 32 == 0 && ldc % 8 == 0; }
+int ggb_gemm_grouped_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t n_rows, int n_exp, const int32_t *offsets, float *c,
+                          void *c_act, int64_t ldc) {
+    GGB_REQUIRE_INIT();
+    static bool attr_done = false;
+    if (!attr_done) {
+        GGB_CUDA(cudaFuncSetAttribute(gemm_bf16w_kernel<GGB_TYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+        attr_done = true;
+    }
+    GemmArgs A{};
+    A.seg[0] = GemmSeg{reinterpret_cast<const uint8_t *>(w), nullptr, c, (int)ldc, 0, (int)N};
+    A.n_seg = 1;
+    A.N = (int)N; A.K = (int)K; A.nb = (int)(K / 32);
+    A.a = (const __nv_bfloat16 *)a; A.T = (int)n_rows;
+    A.kblocks_per_split = (int)(K / BK);
+    A.m_ranges = offsets;
+    A.act_out = (__nv_bfloat16 *)c_act;
+    const dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((n_rows + BM - 1) / BM), (unsigned)n_exp);
+    gemm_bf16w_kernel<GGB_TYPE_BF16><<<grid, kGemmThreads, kGemmSmem, ggb_cuda_stream()>>>(A);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
 
 // the GEMM on plain bf16 matrices (both operands copied by cp.async, nothing to dequantise): the matrix is described
 // as a ggb_weight of type BF16 whose payload plane is the matrix itself.  The K-split workspace belongs to the library

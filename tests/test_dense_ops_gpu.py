@@ -200,7 +200,8 @@ def test_latent_attention_sink_takes_the_weight(gpu, dt):
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
-@pytest.mark.parametrize("T,E,top,Fe,W", [(1, 5, 2, 24, 40), (37, 12, 3, 20, 33), (200, 4, 1, 70, 48), (9, 3, 3, 8, 16), (4, 6, 3, 16, 32), (2, 7, 2, 9, 13)])
+@pytest.mark.parametrize("T,E,top,Fe,W", [(1, 5, 2, 24, 40), (37, 12, 3, 20, 33), (200, 4, 1, 70, 48), (9, 3, 3, 8, 16), (4, 6, 3, 16, 32), (2, 7, 2, 9, 13),
+                                          (300, 4, 2, 64, 128), (700, 6, 1, 96, 192), (1500, 3, 2, 128, 64)])
 def test_mixture_of_experts(gpu, dt, T, E, top, Fe, W):
     r = np.random.default_rng(T + E)
     L = gpu.cuda_lib()
