@@ -128,10 +128,15 @@ template <> struct TileWord<float> {
     static __device__ __forceinline__ float dot(uint32_t w, const float *q, float acc) { return fmaf(__uint_as_float(w), q[0], acc); }
     // accumulator i of a lane holds coordinate coord(lane, i) of sum_j p_j c_j
     static __device__ __forceinline__ int coord(int lane, int i) { return lane + 32 * i; }
-    template <int RC> static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, float pj, float (&acc)[RC]) {
+    template <int RC, int TQ>
+    static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, const float (&pj)[TQ], float (&acc)[TQ][RC]) {
 #pragma unroll
         for (int i = 0; i < RC; i++)
-            if (lane + 32 * i < R) acc[i] = fmaf(pj, __uint_as_float(row[lane + 32 * i]), acc[i]);
+            if (lane + 32 * i < R) {
+                const float c = __uint_as_float(row[lane + 32 * i]);
+#pragma unroll
+                for (int u = 0; u < TQ; u++) acc[u][i] = fmaf(pj[u], c, acc[u][i]);
+            }
     }
     // four words against q[0 .. 4)
     static __device__ __forceinline__ void dot4(const uint32_t *w, const float *q, float (&a)[4]) {
@@ -150,14 +155,19 @@ template <> struct TileWord<__nv_bfloat16> {
     }
     // a lane owns the two numbers of word lane + 32 k: accumulators 2k and 2k + 1 (one 32-bit read for both)
     static __device__ __forceinline__ int coord(int lane, int i) { return 2 * (lane + 32 * (i >> 1)) + (i & 1); }
-    template <int RC> static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, float pj, float (&acc)[RC]) {
+    template <int RC, int TQ>
+    static __device__ __forceinline__ void pv(const uint32_t *row, int lane, int R, const float (&pj)[TQ], float (&acc)[TQ][RC]) {
 #pragma unroll
         for (int k = 0; k < RC / 2; k++) {
             const int w = lane + 32 * k;
             if (2 * w < R) { // R odd: the upper half of the last word is the first number of kr; its accumulator is not stored
                 const uint32_t v = row[w];
-                acc[2 * k] = fmaf(pj, __uint_as_float(v << 16), acc[2 * k]);
-                acc[2 * k + 1] = fmaf(pj, __uint_as_float(v & 0xffff0000u), acc[2 * k + 1]);
+                const float c0 = __uint_as_float(v << 16), c1 = __uint_as_float(v & 0xffff0000u);
+#pragma unroll
+                for (int u = 0; u < TQ; u++) {
+                    acc[u][2 * k] = fmaf(pj[u], c0, acc[u][2 * k]);
+                    acc[u][2 * k + 1] = fmaf(pj[u], c1, acc[u][2 * k + 1]);
+                }
             }
         }
     }
@@ -175,33 +185,43 @@ template <> struct TileWord<__nv_bfloat16> {
     }
 };
 
-template <typename E, int RC>
+template <typename E, int RC, int TQ>
 __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *__restrict__ qa, const E *__restrict__ cache, int64_t ldk,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
-                                                                  int H, int R, int Dr, int n_split, int SW, int hpc, float *__restrict__ part) {
+                                                                  int T, int H, int R, int Dr, int n_split, int SW, int hpc,
+                                                                  float *__restrict__ part) {
+    // TQ consecutive tokens per CTA (portions): a warp scores and accumulates its head for all of them from ONE read of
+    // every tile word; the later token's extra position is masked for the earlier one.
     extern __shared__ __align__(16) uint32_t la_smem[];
     __shared__ int64_t rowoff[32];
     constexpr int PER = TileWord<E>::per;
     const int QK = R + Dr, words = (QK + PER - 1) / PER;
     const int QKp = (words + 3) / 4 * 4 * PER; // q rows padded with zeros to whole groups of four words, 16-byte aligned
     uint32_t *tile = la_smem;                                     // [32][SW]
-    float *qsm = reinterpret_cast<float *>(la_smem + 32 * SW);     // [NW][QKp]; 32 * SW words = 128 * SW bytes: 16-byte aligned
+    float *qsm = reinterpret_cast<float *>(la_smem + 32 * SW);     // [NW][TQ][QKp]; 32 * SW words = 128 * SW bytes: 16-byte aligned
     const int NW = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x, split = blockIdx.y;
-    const int64_t n_kv = (int64_t)*pos0 + t + 1; // causal: the token sees itself and everything before
+    const int t0 = blockIdx.x * TQ, split = blockIdx.y;
+    const int nq = min(TQ, T - t0);
+    const int64_t n_kv0 = (int64_t)*pos0 + t0 + 1; // causal: token t0 + u sees positions < n_kv0 + u
     // tiles of 32 positions are dealt to the splits in turn: split s takes tiles s, s + n_split, ...
-    const int64_t j0 = (int64_t)split * 32, j1 = n_kv, jstep = (int64_t)32 * n_split;
+    const int64_t j0 = (int64_t)split * 32, j1 = n_kv0 + nq - 1, jstep = (int64_t)32 * n_split;
     const int h_begin = blockIdx.z * hpc, h_end = min(H, h_begin + hpc);
     for (int h0 = h_begin; h0 < h_end; h0 += NW) {
         const int h = h0 + warp;
         const bool live = h < h_end;
         __syncthreads(); // the previous group's q and tile are no longer read
-        for (int k = lane; k < QKp; k += 32) // every warp stages its own head
-            qsm[warp * QKp + k] = (live && k < QK) ? qa[((int64_t)t * H + h) * QK + k] : 0.f;
-        float m = -INFINITY, l = 0.f, acc[RC];
 #pragma unroll
-        for (int i = 0; i < RC; i++) acc[i] = 0.f;
-        const float *qh = qsm + warp * QKp;
+        for (int u = 0; u < TQ; u++)
+            for (int k = lane; k < QKp; k += 32) // every warp stages its own head
+                qsm[(warp * TQ + u) * QKp + k] = (live && u < nq && k < QK) ? qa[((int64_t)(t0 + u) * H + h) * QK + k] : 0.f;
+        float m[TQ], l[TQ], acc[TQ][RC];
+#pragma unroll
+        for (int u = 0; u < TQ; u++) {
+            m[u] = -INFINITY, l[u] = 0.f;
+#pragma unroll
+            for (int i = 0; i < RC; i++) acc[u][i] = 0.f;
+        }
+        const float *qh = qsm + warp * TQ * QKp;
         for (int64_t j = j0; j < j1; j += jstep) {
             __syncthreads();
             const int rows = (int)min((int64_t)32, j1 - j);
@@ -238,40 +258,61 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
             }
             __syncthreads();
             if (!live) continue;
-            float s = -INFINITY;
+            float s[TQ];
+#pragma unroll
+            for (int u = 0; u < TQ; u++) s[u] = -INFINITY;
             if (lane < rows) {
                 const uint32_t *tr = tile + lane * SW;
-                float a4[4] = {0.f, 0.f, 0.f, 0.f};
+                float a4[TQ][4];
+#pragma unroll
+                for (int u = 0; u < TQ; u++) a4[u][0] = a4[u][1] = a4[u][2] = a4[u][3] = 0.f;
                 int w = 0;
 #pragma unroll 2
                 for (; w + 3 < words; w += 4) {
                     const uint32_t tw[4] = {tr[w], tr[w + 1], tr[w + 2], tr[w + 3]};
-                    TileWord<E>::dot4(tw, qh + w * PER, a4);
-                }
-                for (; w < words; w++) a4[0] = TileWord<E>::dot(tr[w], qh + w * PER, a4[0]);
-                s = (a4[0] + a4[1]) + (a4[2] + a4[3]);
-            }
-            const float m_new = fmaxf(m, warp_max_f32(s));
-            const float corr = expf(m - m_new), p = expf(s - m_new); // exp(-inf) = 0: first tile, rows past the end
-            l = fmaf(l, corr, warp_sum_f32(p));
-            m = m_new;
 #pragma unroll
-            for (int i = 0; i < RC; i++) acc[i] *= corr;
+                    for (int u = 0; u < TQ; u++) TileWord<E>::dot4(tw, qh + u * QKp + w * PER, a4[u]);
+                }
+                for (; w < words; w++)
+#pragma unroll
+                    for (int u = 0; u < TQ; u++) a4[u][0] = TileWord<E>::dot(tr[w], qh + u * QKp + w * PER, a4[u][0]);
+#pragma unroll
+                for (int u = 0; u < TQ; u++)
+                    if (j + lane < n_kv0 + u && u < nq) s[u] = (a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]);
+            }
+            float p[TQ];
+#pragma unroll
+            for (int u = 0; u < TQ; u++) {
+                const float m_new = fmaxf(m[u], warp_max_f32(s[u]));
+                const float base = m_new == -INFINITY ? 0.f : m_new; // nothing visible yet: exp(-inf - 0) = 0 everywhere
+                const float corr = expf(m[u] - base);
+                p[u] = expf(s[u] - base);
+                l[u] = fmaf(l[u], corr, warp_sum_f32(p[u]));
+                m[u] = m_new;
+#pragma unroll
+                for (int i = 0; i < RC; i++) acc[u][i] *= corr;
+            }
             for (int jj = 0; jj < rows; jj++) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
-                TileWord<E>::template pv<RC>(tile + jj * SW, lane, R, pj, acc);
+                float pj[TQ];
+#pragma unroll
+                for (int u = 0; u < TQ; u++) pj[u] = __shfl_sync(0xffffffffu, p[u], jj);
+                TileWord<E>::template pv<RC, TQ>(tile + jj * SW, lane, R, pj, acc);
             }
         }
         if (live) {
-            float *o = part + (((int64_t)t * n_split + split) * H + h) * (R + 2);
-            if (lane == 0) {
-                o[0] = m;
-                o[1] = l;
-            }
 #pragma unroll
-            for (int i = 0; i < RC; i++) {
-                const int r = TileWord<E>::coord(lane, i);
-                if (r < R) o[2 + r] = acc[i];
+            for (int u = 0; u < TQ; u++) {
+                if (u >= nq) continue;
+                float *o = part + (((int64_t)(t0 + u) * n_split + split) * H + h) * (R + 2);
+                if (lane == 0) {
+                    o[0] = m[u];
+                    o[1] = l[u];
+                }
+#pragma unroll
+                for (int i = 0; i < RC; i++) {
+                    const int r = TileWord<E>::coord(lane, i);
+                    if (r < R) o[2 + r] = acc[u][i];
+                }
             }
         }
     }
@@ -323,7 +364,9 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
 #pragma unroll
         for (int tt = 0; tt < kOutT; tt++) acc[tt] = 0.f;
         constexpr int VE = 16 / (int)sizeof(E);
-        if (R % VE == 0 && (reinterpret_cast<uintptr_t>(w_uv) & 15) == 0) {
+        // few CTAs (decode): 16-byte loads, everything in flight at once; a full grid is better off with the conflict-free
+        // 4-byte reads of shared memory
+        if (v_chunk < Dv && R % VE == 0 && (reinterpret_cast<uintptr_t>(w_uv) & 15) == 0) {
 #pragma unroll 4
             for (int k = lane * VE; k < R; k += 32 * VE) {
                 const uint4 wv = *reinterpret_cast<const uint4 *>(wr + k);
@@ -368,20 +411,27 @@ int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const i
     // handful of tokens must fill it (the tile is then staged once per group)
     const int hpc = T >= 64 ? H : (H < 4 ? H : 4);
     const int NW = hpc < 16 ? hpc : 16;
-    const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * ((words + 3) / 4 * 4) * PER * 4;
+    const int tq = (T >= 64 && R <= 512) ? 2 : 1; // two tokens per CTA for portions (their accumulators fit the registers)
+    const size_t smem = (size_t)32 * SW * 4 + (size_t)NW * tq * ((words + 3) / 4 * 4) * PER * 4;
     GGB_CHECK_ARG(smem <= 200 * 1024, "latent_attn: rows of %d numbers do not fit shared memory", R + Dr);
-    const dim3 grid((unsigned)T, (unsigned)n_split, (unsigned)((H + hpc - 1) / hpc));
-#define LA_CASE(RC)                                                                                                          \
+    const dim3 grid((unsigned)((T + tq - 1) / tq), (unsigned)n_split, (unsigned)((H + hpc - 1) / hpc));
+#define LA_LAUNCH(RC, TQ)                                                                                                    \
     {                                                                                                                        \
-        auto k = latent_attn_partial_kernel<E, RC>;                                                                          \
+        auto k = latent_attn_partial_kernel<E, RC, TQ>;                                                                      \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, H, R, Dr, n_split, SW, hpc, part); \
+        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, (int)T, H, R, Dr, n_split, SW, hpc, part); \
+    }
+#define LA_CASE(RC)                       \
+    {                                     \
+        if (tq == 2) LA_LAUNCH(RC, 2)     \
+        else LA_LAUNCH(RC, 1)             \
     }
     if (R <= 64) LA_CASE(2)
     else if (R <= 128) LA_CASE(4)
     else if (R <= 256) LA_CASE(8)
     else if (R <= 512) LA_CASE(16)
-    else LA_CASE(32)
+    else LA_LAUNCH(32, 1)
+#undef LA_LAUNCH
 #undef LA_CASE
     GGB_LAUNCH_CHECK();
     return GGB_OK;
