@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(256) linear_vec_kernel(const E *__restrict__ w
     const bool vec = (K % VE == 0) && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(a)) % 16 == 0) &&
                      (lda % VE == 0);
     if (vec) {
-        for (int64_t k = (int64_t)lane * VE; k < K; k += 32 * VE) {
+#pragma unroll 4
+        for (int64_t k = (int64_t)lane * VE; k < K; k += 32 * VE) { // several 16-byte loads of the row in flight
             const uint4 wv = ldg_stream_u4(wr + k);
             const E *we = reinterpret_cast<const E *>(&wv);
             float wf[VE];
