@@ -107,7 +107,7 @@ def matvec_bytes_per_step(dims, wtype):
 
 def cpu_reference_tokens_per_s(args, n_tokens, warm=1, budget_s=None):
     """The reference's CPU path restated by the oracle (thread_pool row split, scalar vec_dot), on the
-    same workload; ORACLE USE: this is the checker timed as a baseline, never the product.
+    same workload; ORACLE USE: this is the oracle timed as a baseline, never the product.
     budget_s bounds the timed region: tokens stop early once it is spent (the count actually timed is
     returned), so the run ends within minutes whatever the host's core count."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -360,7 +360,7 @@ def run_ours(args):
             torch.cuda.synchronize()
 
     # ---- multi-GPU: parity first (tiny MQA + MHA models, both quant types, fused lowering, against the oracle, bit for
-    # bit) - ORACLE USE: the checker, before and outside every timed region
+    # bit) - ORACLE USE: the oracle, before and outside every timed region
     tp_parity = None
     if world > 1:
         sys.path.insert(0, os.path.join(ROOT, "tests"))

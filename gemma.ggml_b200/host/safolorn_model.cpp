@@ -85,7 +85,7 @@ int sf_parse_config(const json_value &j, sf_config *c, std::string *err) {
             if (kind == "dense") {
                 l.mlp = 1;
                 l.ff = (int)f->integer("ff", 0);
-                l.limit = (float)f->number("limit", 0.0);
+                l.limit = f->get("limit") ? (float)f->number("limit", 0.0) : INFINITY; // no limit named: nothing is clamped
             } else if (kind == "moe") {
                 l.mlp = 2;
                 const json_value *e = f->get("expert"), *r = f->get("router");
