@@ -146,6 +146,27 @@ def test_other_sizes(gpu, tmp_path, name, dtype):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_reach_the_tensor_core_products(gpu, tmp_path, dtype):
+    """Width, feed-forward and latent sizes in multiples of 64 and a portion of several hundred tokens: in bfloat16 the
+    products run as tcgen05 GEMMs (plain and grouped by expert), the attention takes two tokens per CTA; then portions
+    that fall back to the tile kernel and the mat-vec, all against the oracle."""
+    cfg = F.config([F.layer(F.mixer(heads=5, dim=24, rot_dim=16, vdim=40, kv_rank=96, scale=0.15), F.moe(ff=64, experts=6, top=2)),
+                    F.layer(F.mixer(heads=3, dim=32, rot_dim=16, vdim=64, kv_rank=96, scale=0.15, kv_from=0), F.dense(ff=320, limit=1.5)),
+                    F.layer(F.mixer(heads=4, dim=16, rot_dim=32, vdim=16, kv_rank=64, scaling=False), F.moe(ff=128, experts=3, top=1))],
+                   vocab=160, width=192, side=24)
+    d, W = F.make_model(str(tmp_path / "m"), cfg, seed=21)
+    toks = np.random.default_rng(4).integers(0, cfg["vocab"], 460)
+    want = plain_logits(cfg, W, toks)
+    eng = gpu.Engine(d, dtype=dtype, max_tokens=512, page_size=64)
+    a = eng.step([("a", toks[:330], np.arange(330))])
+    b = eng.step([("a", toks[330:400], np.arange(70))])
+    c = eng.step([("a", toks[400:437], np.arange(37))])
+    e = np.concatenate([eng.step([("a", toks[i:i + 1], [0])]) for i in range(437, 460)])
+    assert F.close_enough(np.concatenate([a, b, c, e]), want, dtype)
+    eng.close()
+
+
 def test_random_weight_engine_and_registry(gpu):
     cfg = F.small_config()
     eng = gpu.Engine(config=cfg, seed=4, dtype="bfloat16", max_tokens=64)
