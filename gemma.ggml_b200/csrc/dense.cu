@@ -220,30 +220,52 @@ __global__ void __launch_bounds__(512) residual_side_kernel(float *__restrict__ 
     }
     if (!sd) return;
     __syncthreads();
-    for (int i = warp; i < sd; i += nwarp) { // gate: a warp per output, the row of w_gate read once for the TT tokens
-        float s[TT];
+    // gate: a warp takes GQ outputs at a time (rows i, i + nwarp, ...): their loads are independent and in flight together;
+    // every row of w_gate is read once for the TT tokens
+    constexpr int GQ = TT >= 4 ? 2 : 4;
+    for (int i0 = warp; i0 < sd; i0 += nwarp * GQ) {
+        float s[GQ][TT];
 #pragma unroll
-        for (int tt = 0; tt < TT; tt++) s[tt] = 0.f;
-        const E *wr = w_gate + (int64_t)i * W;
+        for (int g = 0; g < GQ; g++)
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) s[g][tt] = 0.f;
         if (vec) {
-#pragma unroll 4
+#pragma unroll 2
             for (int64_t k = (int64_t)lane * VN; k < W; k += 32 * VN) {
-                Vec16<E> v;
-                v.raw = *reinterpret_cast<const uint4 *>(wr + k);
+                Vec16<E> v[GQ];
+#pragma unroll
+                for (int g = 0; g < GQ; g++) {
+                    const int i = min(i0 + g * nwarp, sd - 1); // a row past the end repeats the last one; its sum is dropped
+                    v[g].raw = *reinterpret_cast<const uint4 *>(w_gate + (int64_t)i * W + k);
+                }
 #pragma unroll
                 for (int u = 0; u < VN; u++)
 #pragma unroll
-                    for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(v.at(u), xs[tt * W + k + u], s[tt]);
+                    for (int tt = 0; tt < TT; tt++) {
+                        const float xv = xs[tt * W + k + u];
+#pragma unroll
+                        for (int g = 0; g < GQ; g++) s[g][tt] = fmaf(v[g].at(u), xv, s[g][tt]);
+                    }
             }
         } else {
             for (int64_t k = lane; k < W; k += 32)
 #pragma unroll
-                for (int tt = 0; tt < TT; tt++) s[tt] = fmaf(to_f32(wr[k]), xs[tt * W + k], s[tt]);
+                for (int g = 0; g < GQ; g++) {
+                    const int i = min(i0 + g * nwarp, sd - 1);
+                    const float wv = to_f32(w_gate[(int64_t)i * W + k]);
+#pragma unroll
+                    for (int tt = 0; tt < TT; tt++) s[g][tt] = fmaf(wv, xs[tt * W + k], s[g][tt]);
+                }
         }
 #pragma unroll
-        for (int tt = 0; tt < TT; tt++) {
-            const float r = warp_sum_f32(s[tt]);
-            if (lane == 0 && tt < nt) gs[tt * sd + i] = gelu_tanh_f32(r) * to_f32(side_embed[(int64_t)ids[t0 + tt] * e_ld + e_off + i]);
+        for (int g = 0; g < GQ; g++) {
+            const int i = i0 + g * nwarp;
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) {
+                const float r = warp_sum_f32(s[g][tt]);
+                if (lane == 0 && tt < nt && i < sd)
+                    gs[tt * sd + i] = gelu_tanh_f32(r) * to_f32(side_embed[(int64_t)ids[t0 + tt] * e_ld + e_off + i]);
+            }
         }
     }
     __syncthreads();
