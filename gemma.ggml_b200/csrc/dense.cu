@@ -459,3 +459,182 @@ int ggb_op_cvt_bf16_f32(const void *x_bf16, int64_t n, float *y) {
 }
 
 } // extern "C"
+
+// ------------------------------------------------------------------------------------------------ grouped norms, gates, bigram rows
+namespace {
+
+__device__ __forceinline__ float block_sum_256(float v, float *red) { // all threads get the sum; blockDim.x == 256
+    v = warp_sum_f32(v);
+    __syncthreads(); // `red` may still be read by the previous call
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += red[i];
+    return tot;
+}
+
+// one CTA per token: the embedding row plus the row of the hashed pair (previous token, token)
+template <typename E>
+__global__ void __launch_bounds__(256) embed_bigram_kernel(const E *__restrict__ table, const E *__restrict__ bigram,
+                                                           const int32_t *__restrict__ ids, int64_t T, int64_t n, long long buckets,
+                                                           long long mul_prev, long long mul_cur, const int32_t *__restrict__ pos0,
+                                                           int32_t *prev_state, float *__restrict__ y) {
+    const int64_t t = blockIdx.x;
+    const long long id = ids[t];
+    const long long prev = t > 0 ? (long long)ids[t - 1] : (long long)*prev_state;
+    const long long row = ((long long)*pos0 + t == 0) ? buckets : (prev * mul_prev + id * mul_cur) % buckets;
+    const E *e = table + id * n, *b = bigram + row * n;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[t * n + i] = to_f32(e[i]) + to_f32(b[i]);
+    if (t == 0) { // only this CTA touches the carried token: it has read it above
+        __syncthreads();
+        if (threadIdx.x == 0) *prev_state = ids[T - 1];
+    }
+}
+
+// one CTA per token; the row lives in shared memory between the two passes
+template <typename E>
+__global__ void __launch_bounds__(256) group_norm_add_kernel(const float *__restrict__ a, float sa, const float *__restrict__ b, float sb,
+                                                             const float *__restrict__ bias, const float *__restrict__ w, int groups,
+                                                             float eps, int64_t n, float *x, E *__restrict__ y) {
+    extern __shared__ float gn_row[];
+    __shared__ float red[8];
+    const int64_t t = blockIdx.x, gs = n / groups;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = sa * a[t * n + i];
+        if (b) v += sb * b[t * n + i];
+        if (bias) v += bias[i];
+        gn_row[i] = v;
+    }
+    __syncthreads();
+    for (int g = 0; g < groups; g++) {
+        float ss = 0.f;
+        for (int64_t i = threadIdx.x; i < gs; i += blockDim.x) ss = fmaf(gn_row[g * gs + i], gn_row[g * gs + i], ss);
+        const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)gs + eps);
+        for (int64_t i = g * gs + threadIdx.x; i < (g + 1) * gs; i += blockDim.x) {
+            float v = gn_row[i] * r * w[i];
+            if (x) {
+                v += x[t * n + i];
+                x[t * n + i] = v;
+            }
+            if (y) y[t * n + i] = from_f32<E>(v);
+        }
+    }
+}
+
+template <typename E>
+__global__ void glu_bias_kernel(const float *__restrict__ gu, int64_t F, int64_t T, const float *__restrict__ bg, const float *__restrict__ bu,
+                                int act, E *__restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * F) return;
+    const int64_t t = i / F, f = i - t * F;
+    float g = gu[t * 2 * F + f], u = gu[t * 2 * F + F + f];
+    if (bg) g += bg[f];
+    if (bu) u += bu[f];
+    if (act == 0) g = fmaxf(g, 0.f);
+    else if (act == 1) g = g / (1.0f + expf(-g));
+    else g = gelu_tanh_f32(g);
+    y[i] = from_f32<E>(g * u);
+}
+
+__global__ void softcap_kernel(float *x, int64_t n, float cap) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+// a warp per (token, group): o / rms(o) * w * act(gate)
+template <typename E>
+__global__ void __launch_bounds__(256) norm_gate_kernel(const float *__restrict__ o, int64_t ldo, const float *__restrict__ gate, int64_t ldg,
+                                                        int64_t T, int n_groups, int gs, const float *__restrict__ w, int w_period, float eps,
+                                                        int act, E *__restrict__ y) {
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= T * n_groups) return;
+    const int64_t t = item / n_groups;
+    const int g = (int)(item - t * n_groups), lane = threadIdx.x & 31;
+    const float *orow = o + t * ldo + (int64_t)g * gs, *grow = gate + t * ldg + (int64_t)g * gs;
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) ss = fmaf(orow[i], orow[i], ss);
+    const float r = 1.0f / sqrtf(warp_sum_f32(ss) / (float)gs + eps);
+    for (int i = lane; i < gs; i += 32) {
+        const float z = grow[i];
+        const float s = 1.0f / (1.0f + expf(-z));
+        y[(t * n_groups + g) * gs + i] = from_f32<E>(orow[i] * r * w[(g * gs + i) % w_period] * (act == 1 ? z * s : s));
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+int ggb_op_embed_bigram(int dt, const void *table, const void *bigram, const int32_t *ids, int64_t T, int64_t E, int64_t buckets,
+                        int64_t mul_prev, int64_t mul_cur, const int32_t *pos0, int32_t *prev_state, float *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(table && bigram && ids && pos0 && prev_state && y && T > 0 && E > 0 && buckets > 0, "embed_bigram: bad arguments");
+    if (dt == GGB_TYPE_BF16)
+        embed_bigram_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)table, (const __nv_bfloat16 *)bigram, ids, T, E,
+                                                                        (long long)buckets, (long long)mul_prev, (long long)mul_cur, pos0,
+                                                                        prev_state, y);
+    else
+        embed_bigram_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const float *)table, (const float *)bigram, ids, T, E, (long long)buckets,
+                                                                        (long long)mul_prev, (long long)mul_cur, pos0, prev_state, y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_group_norm_add(int dt, const float *a, float sa, const float *b, float sb, const float *bias, const float *w, int groups,
+                          float eps, int64_t E, int64_t T, float *x, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(a && w && E > 0 && T > 0 && groups > 0 && E % groups == 0 && (x || y), "group_norm_add: bad arguments (width %lld, %d groups)",
+                  (long long)E, groups);
+    const size_t smem = (size_t)E * 4;
+    GGB_CHECK_ARG(smem <= 200 * 1024, "group_norm_add: width %lld does not fit shared memory", (long long)E);
+#define GN_LAUNCH(ET)                                                                                                          \
+    {                                                                                                                          \
+        auto k = group_norm_add_kernel<ET>;                                                                                    \
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
+        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(a, sa, b, sb, bias, w, groups, eps, E, x, (ET *)y);                    \
+    }
+    if (dt == GGB_TYPE_BF16) GN_LAUNCH(__nv_bfloat16) else GN_LAUNCH(float)
+#undef GN_LAUNCH
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_glu_bias(int dt, const float *gu, int64_t F, int64_t T, const float *bg, const float *bu, int act, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(gu && y && F > 0 && T > 0 && act >= 0 && act <= 2, "glu_bias: bad arguments");
+    const unsigned blocks = (unsigned)((T * F + 255) / 256);
+    if (dt == GGB_TYPE_BF16) glu_bias_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(gu, F, T, bg, bu, act, (__nv_bfloat16 *)y);
+    else glu_bias_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(gu, F, T, bg, bu, act, (float *)y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_softcap(float *x, int64_t n, float cap) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(x && n > 0 && cap > 0.f, "softcap: bad arguments");
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ggb_cuda_stream()>>>(x, n, cap);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int64_t ldg, int64_t T, int n_groups, int gs, const float *w,
+                     int w_period, float eps, int act, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(o && gate && w && y && T > 0 && n_groups > 0 && gs > 0 && w_period > 0 && ldo >= (int64_t)n_groups * gs &&
+                      ldg >= (int64_t)n_groups * gs && (act == 0 || act == 1),
+                  "norm_gate: bad arguments");
+    const unsigned blocks = (unsigned)((T * n_groups + 7) / 8);
+    if (dt == GGB_TYPE_BF16)
+        norm_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (__nv_bfloat16 *)y);
+    else
+        norm_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (float *)y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

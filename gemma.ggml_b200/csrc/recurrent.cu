@@ -1,0 +1,284 @@
+// recurrent.cu — mixers whose memory is a fixed-size state instead of a row per position: the causal convolution over
+// time with a carried tail, lightning attention (a decayed sum of outer products) and the gated delta rule.  All state
+// is fp32 and lives in the caller's per-sequence block; a portion of T tokens continues from the state the previous
+// portion left and leaves its own, so a prompt may be cut anywhere.
+//
+// The two recurrences share one kernel: a CTA owns one head and a slice of CV value columns (columns are independent
+// in both rules), NS lanes share a column and each keeps D / NS numbers of it in registers for the whole portion.
+// Per token the lanes' partial sums meet through two shuffles.  Tokens are staged through shared memory in chunks;
+// the staging pass also does what is per token and parallel: activations, unit norms, decay and step size.
+//
+// Compiled with -fmad=false: multiply-adds are spelled fmaf().
+#include "common.cuh"
+#include "dense.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f32(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// ------------------------------------------------------------------------------------------------ causal convolution
+constexpr int kConvMaxTaps = 8, kConvTokens = 32;
+
+// grid (channel blocks, token chunks); a thread owns one channel of one chunk and slides a window of taps inputs along
+// it.  Chunk 0 is the only reader of the old tail and its only writer (after it has the old values in registers).
+template <typename E>
+__global__ void __launch_bounds__(128) causal_conv_kernel(const float *__restrict__ x, int64_t ldx, int64_t T, int64_t C,
+                                                          const float *__restrict__ w, int taps, int add_input, int act, float *tail,
+                                                          float *__restrict__ y_f32, int64_t ldy, E *__restrict__ y_dt) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int64_t t0 = (int64_t)blockIdx.y * kConvTokens, t1 = min(T, t0 + kConvTokens);
+    const int nt = taps - 1;
+    float wt[kConvMaxTaps], win[kConvMaxTaps], old[kConvMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; j++) {
+        wt[j] = j < taps ? w[c * taps + j] : 0.f;
+        win[j] = 0.f;
+        old[j] = 0.f;
+    }
+    if (blockIdx.y == 0)
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; j++)
+            if (j < nt) old[j] = tail[(int64_t)j * C + c];
+    // win[j], j < taps - 1: the inputs at t0 - (taps - 1) + j
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 1; j++)
+        if (j < nt) {
+            const int64_t s = t0 - nt + j;
+            win[j] = s >= 0 ? x[s * ldx + c] : old[j]; // s < 0 only in chunk 0, where s + nt = j indexes the old tail
+        }
+    for (int64_t t = t0; t < t1; t++) {
+        const float xv = x[t * ldx + c];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; j++)
+            if (j < nt) acc = fmaf(wt[j], win[j], acc);
+        acc = fmaf(wt[nt], xv, acc);
+        if (add_input) acc += xv;
+        if (act) acc = silu_f32(acc);
+        if (y_f32) y_f32[t * ldy + c] = acc;
+        if (y_dt) y_dt[t * C + c] = from_f32<E>(acc);
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 2; j++)
+            if (j + 1 < nt) win[j] = win[j + 1];
+        if (nt > 0) {
+#pragma unroll
+            for (int j = 0; j < kConvMaxTaps - 1; j++)
+                if (j == nt - 1) win[j] = xv;
+        }
+    }
+    if (blockIdx.y == 0) { // new tail: the last taps - 1 inputs of (old tail, x)
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; j++)
+            if (j < nt) {
+                const int64_t s = T - nt + j;
+                float v = 0.f;
+                if (s >= 0) v = x[s * ldx + c];
+                else {
+#pragma unroll
+                    for (int i = 0; i < kConvMaxTaps - 1; i++)
+                        if (i == (int)(s + nt)) v = old[i];
+                }
+                tail[(int64_t)j * C + c] = v;
+            }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ the recurrences
+constexpr int kNS = 4;      // lanes that share a column of S
+constexpr int kCV = 32;     // value columns per CTA (kCV * kNS = 128 threads)
+constexpr int kChunk = 16;  // tokens staged at once
+
+struct rec_args {
+    const float *q, *k, *v, *b, *a;
+    int64_t ld, ld_ba, T;
+    int H, G, D, Dv;
+    const float *decay, *A_log, *dt_bias;
+    float *state, *o;
+    int64_t ldo;
+};
+
+// MODE 0: lightning (q, k, v = silu of the raw rows; S <- decay S + k v^T; o = S^T q)
+// MODE 1: gated delta rule (unit q and k, q * D^-1/2; S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q)
+template <int DS, int MODE>
+__global__ void __launch_bounds__(kCV *kNS) recurrence_kernel(rec_args p) {
+    constexpr int DP = DS * kNS; // padded D
+    __shared__ __align__(16) float sq[kChunk][DP], sk[kChunk][DP];
+    __shared__ float sv[kChunk][kCV], sg[kChunk], sbeta[kChunk];
+    const int h = blockIdx.x, col0 = blockIdx.y * kCV;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = tid % kNS, cl = tid / kNS, col = col0 + cl;
+    const bool live = col < p.Dv;
+    const int hk = MODE == 1 ? h / (p.H / p.G) : h; // the q / k head this head reads
+    float S[DS];
+    float *sp = p.state + ((int64_t)h * p.D) * p.Dv + col;
+#pragma unroll
+    for (int i = 0; i < DS; i++) {
+        const int d = s * DS + i;
+        S[i] = (live && d < p.D) ? sp[(int64_t)d * p.Dv] : 0.f;
+    }
+    const float decay = MODE == 0 ? p.decay[h] : 0.f;
+    const float a_rate = MODE == 1 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
+    const float q_scale = 1.0f / sqrtf((float)p.D);
+    for (int64_t t0 = 0; t0 < p.T; t0 += kChunk) {
+        const int n = (int)min((int64_t)kChunk, p.T - t0);
+        __syncthreads(); // the previous chunk has been consumed
+        // stage: a warp takes tokens warp, warp + 4, ...
+        for (int tt = warp; tt < n; tt += (kCV * kNS) / 32) {
+            const float *qr = p.q + (t0 + tt) * p.ld + (int64_t)hk * p.D, *kr = p.k + (t0 + tt) * p.ld + (int64_t)hk * p.D;
+            float qs = 0.f, ks = 0.f;
+            for (int d = lane; d < DP; d += 32) {
+                float qv = 0.f, kv = 0.f;
+                if (d < p.D) {
+                    qv = qr[d];
+                    kv = kr[d];
+                    if (MODE == 0) {
+                        qv = silu_f32(qv);
+                        kv = silu_f32(kv);
+                    }
+                }
+                sq[tt][d] = qv;
+                sk[tt][d] = kv;
+                qs = fmaf(qv, qv, qs);
+                ks = fmaf(kv, kv, ks);
+            }
+            if (MODE == 1) {
+                qs = warp_sum_f32(qs);
+                ks = warp_sum_f32(ks);
+                const float qm = q_scale / sqrtf(qs + 1e-6f), km = 1.0f / sqrtf(ks + 1e-6f);
+                __syncwarp();
+                for (int d = lane; d < DP; d += 32) {
+                    sq[tt][d] *= qm;
+                    sk[tt][d] *= km;
+                }
+                if (lane == 0) {
+                    sbeta[tt] = sigmoid_f32(p.b[(t0 + tt) * p.ld_ba + h]);
+                    sg[tt] = expf(-a_rate * softplus_f32(p.a[(t0 + tt) * p.ld_ba + h] + dtb));
+                }
+            }
+            const float *vr = p.v + (t0 + tt) * p.ld + (int64_t)h * p.Dv + col0;
+            if (lane < kCV) {
+                float vv = col0 + lane < p.Dv ? vr[lane] : 0.f;
+                if (MODE == 0) vv = silu_f32(vv);
+                sv[tt][lane] = vv;
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; tt++) {
+            const float4 *k4 = reinterpret_cast<const float4 *>(&sk[tt][s * DS]);
+            const float4 *q4 = reinterpret_cast<const float4 *>(&sq[tt][s * DS]);
+            float o0 = 0.f, o1 = 0.f;
+            if (MODE == 0) {
+                const float vj = sv[tt][cl];
+#pragma unroll
+                for (int i = 0; i < DS / 4; i++) {
+                    const float4 kk = k4[i], qq = q4[i];
+                    S[4 * i + 0] = fmaf(kk.x, vj, decay * S[4 * i + 0]);
+                    S[4 * i + 1] = fmaf(kk.y, vj, decay * S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(kk.z, vj, decay * S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(kk.w, vj, decay * S[4 * i + 3]);
+                    o0 = fmaf(S[4 * i + 0], qq.x, o0);
+                    o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                    o0 = fmaf(S[4 * i + 2], qq.z, o0);
+                    o1 = fmaf(S[4 * i + 3], qq.w, o1);
+                }
+            } else {
+                const float g = sg[tt];
+                float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DS / 4; i++) {
+                    const float4 kk = k4[i];
+                    S[4 * i + 0] *= g;
+                    S[4 * i + 1] *= g;
+                    S[4 * i + 2] *= g;
+                    S[4 * i + 3] *= g;
+                    r0 = fmaf(S[4 * i + 0], kk.x, r0);
+                    r1 = fmaf(S[4 * i + 1], kk.y, r1);
+                    r0 = fmaf(S[4 * i + 2], kk.z, r0);
+                    r1 = fmaf(S[4 * i + 3], kk.w, r1);
+                }
+                float r = r0 + r1;
+                r += __shfl_xor_sync(0xffffffffu, r, 1);
+                r += __shfl_xor_sync(0xffffffffu, r, 2);
+                const float u = sbeta[tt] * (sv[tt][cl] - r);
+#pragma unroll
+                for (int i = 0; i < DS / 4; i++) {
+                    const float4 kk = k4[i], qq = q4[i];
+                    S[4 * i + 0] = fmaf(kk.x, u, S[4 * i + 0]);
+                    S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
+                    o0 = fmaf(S[4 * i + 0], qq.x, o0);
+                    o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                    o0 = fmaf(S[4 * i + 2], qq.z, o0);
+                    o1 = fmaf(S[4 * i + 3], qq.w, o1);
+                }
+            }
+            float o = o0 + o1;
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (s == 0 && live) p.o[(t0 + tt) * p.ldo + (int64_t)h * p.Dv + col] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DS; i++) {
+        const int d = s * DS + i;
+        if (live && d < p.D) sp[(int64_t)d * p.Dv] = S[i];
+    }
+}
+
+template <int MODE>
+int recurrence_launch(const rec_args &p) {
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + kCV - 1) / kCV));
+    const int ds = (p.D + kNS - 1) / kNS;
+    cudaStream_t st = ggb_cuda_stream();
+    if (ds <= 8) recurrence_kernel<8, MODE><<<grid, kCV * kNS, 0, st>>>(p);
+    else if (ds <= 16) recurrence_kernel<16, MODE><<<grid, kCV * kNS, 0, st>>>(p);
+    else if (ds <= 32) recurrence_kernel<32, MODE><<<grid, kCV * kNS, 0, st>>>(p);
+    else recurrence_kernel<64, MODE><<<grid, kCV * kNS, 0, st>>>(p);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int ggb_op_causal_conv(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, int taps, int add_input, int act,
+                       float *tail, float *y_f32, int64_t ldy, void *y_dt) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "causal_conv: dtype %d is neither bf16 nor f32", dt);
+    GGB_CHECK_ARG(x && w && T > 0 && C > 0 && ldx >= C && taps >= 1 && taps <= kConvMaxTaps && (taps == 1 || tail) && (y_f32 || y_dt) &&
+                      (!y_f32 || ldy >= C),
+                  "causal_conv: bad arguments (taps %d, at most %d)", taps, kConvMaxTaps);
+    const dim3 grid((unsigned)((C + 127) / 128), (unsigned)((T + kConvTokens - 1) / kConvTokens));
+    if (dt == GGB_TYPE_BF16)
+        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, taps, add_input, act, tail, y_f32, ldy, (__nv_bfloat16 *)y_dt);
+    else
+        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, taps, add_input, act, tail, y_f32, ldy, (float *)y_dt);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int D, int Dv, const float *decay,
+                          float *state, float *o, int64_t ldo) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(q && k && v && decay && state && o && T > 0 && H > 0 && D > 0 && D <= 64 * kNS && Dv > 0 && ldo >= (int64_t)H * Dv,
+                  "lightning_attn: bad arguments (key size %d, at most %d)", D, 64 * kNS);
+    rec_args p{q, k, v, nullptr, nullptr, ld, 0, T, H, H, D, Dv, decay, nullptr, nullptr, state, o, ldo};
+    return recurrence_launch<0>(p);
+}
+
+int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, const float *a, int64_t ld_ba, int64_t T,
+                       int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(q && k && v && b && a && A_log && dt_bias && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 64 * kNS &&
+                      Dv > 0 && ldo >= (int64_t)H * Dv,
+                  "gated_delta: bad arguments (heads %d over %d key heads, key size %d)", H, G, D);
+    rec_args p{q, k, v, b, a, ld, ld_ba, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
+    return recurrence_launch<1>(p);
+}
+
+} // extern "C"

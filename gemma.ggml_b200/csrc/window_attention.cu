@@ -1,0 +1,281 @@
+// window_attention.cu — grouped-query soft-max attention over a sliding window of a paged cache, with rotary positions
+// on queries and keys and with rotated values: the value of position j is cached turned by j, the weighted sum of a head
+// is turned back by the reader's position i, so that what a head adds depends on i - j only.
+//
+// The cache row of a position holds [k (G * D) | v (G * Dv)] in the storage type; page tables and positions are read
+// on the device (a captured one-token step replays anywhere).  Scores, soft-max and the weighted sum are fp32.
+//
+// qkv_store: one CTA per token: root mean square over the whole q and the whole k projection, weights, rotation, store.
+// window_attn: a warp owns (token, head[, split of the keys]); lane = key for the scores (its row read with 16-byte
+// loads), lane = pair of value coordinates for the weighted sum (rows read coalesced), running maximum and sum in
+// registers.  Portions: 8 consecutive tokens of one head per CTA (their windows overlap: the rows meet in L1);
+// a step of few tokens: 8 warps split one (token, head)'s keys and merge through shared memory.
+//
+// Compiled with -fmad=false: multiply-adds are spelled fmaf().
+#include "common.cuh"
+#include "dense.cuh"
+
+namespace {
+
+constexpr int kMaxDvRegs = 8; // value coordinates per lane: Dv <= 32 * kMaxDvRegs
+constexpr int kWarps = 8;
+
+template <typename E>
+__global__ void __launch_bounds__(256) window_qkv_store_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                                               int64_t ld, int H, int G, int D, int Dv, const float *__restrict__ qn_w,
+                                                               const float *__restrict__ kn_w, float eps, int rot_dims,
+                                                               const float *__restrict__ cs_k, const float *__restrict__ cs_v, float scale,
+                                                               const int32_t *__restrict__ pos0, const int32_t *__restrict__ table, int B,
+                                                               E *__restrict__ cache, int64_t cache_ld, float *__restrict__ q_out) {
+    __shared__ float red[2][8];
+    const int64_t t = blockIdx.x;
+    const int64_t pos = (int64_t)*pos0 + t;
+    const float *qr = q + t * ld, *kr = k + t * ld, *vr = v + t * ld;
+    const int nq = H * D, nk = G * D, nv = G * Dv;
+    float rq = 1.f, rk = 1.f;
+    if (qn_w || kn_w) {
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) sq = fmaf(qr[i], qr[i], sq);
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) sk = fmaf(kr[i], kr[i], sk);
+        sq = warp_sum_f32(sq);
+        sk = warp_sum_f32(sk);
+        if ((threadIdx.x & 31) == 0) {
+            red[0][threadIdx.x >> 5] = sq;
+            red[1][threadIdx.x >> 5] = sk;
+        }
+        __syncthreads();
+        float tq = 0.f, tk = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            tq += red[0][i];
+            tk += red[1][i];
+        }
+        if (qn_w) rq = 1.0f / sqrtf(tq / (float)nq + eps);
+        if (kn_w) rk = 1.0f / sqrtf(tk / (float)nk + eps);
+    }
+    E *row = cache + ((int64_t)table[pos / B] * B + pos % B) * cache_ld;
+    const float *ck = cs_k ? cs_k + pos * (rot_dims / 2) * 2 : nullptr;
+    // pairs (2i, 2i + 1) of q and k
+    for (int p = threadIdx.x; p < (nq + nk) / 2; p += blockDim.x) {
+        const bool is_q = p < nq / 2;
+        const int e = is_q ? 2 * p : 2 * p - nq; // even coordinate inside the projection
+        const float *src = is_q ? qr : kr;
+        const float *nw = is_q ? qn_w : kn_w;
+        const float r = is_q ? rq : rk;
+        float u = src[e], w = src[e + 1];
+        if (nw) {
+            u = u * r * nw[e];
+            w = w * r * nw[e + 1];
+        }
+        const int d = e % D;
+        if (ck && d < rot_dims) {
+            const float c = ck[d], s = ck[d + 1]; // pair d / 2: [cos, sin]
+            const float u2 = u * c - w * s, w2 = w * c + u * s;
+            u = u2;
+            w = w2;
+        }
+        if (is_q) {
+            q_out[t * nq + e] = u * scale;
+            q_out[t * nq + e + 1] = w * scale;
+        } else {
+            row[e] = from_f32<E>(u);
+            row[e + 1] = from_f32<E>(w);
+        }
+    }
+    const float *cv = cs_v ? cs_v + pos * (Dv / 2) * 2 : nullptr;
+    for (int p = threadIdx.x; p < nv / 2; p += blockDim.x) {
+        const int e = 2 * p, d = e % Dv;
+        float u = vr[e], w = vr[e + 1];
+        if (cv) {
+            const float c = cv[d], s = cv[d + 1];
+            const float u2 = u * c - w * s, w2 = w * c + u * s;
+            u = u2;
+            w = w2;
+        }
+        row[nk + e] = from_f32<E>(u);
+        row[nk + e + 1] = from_f32<E>(w);
+    }
+}
+
+template <typename E> struct RowVec { // 16 bytes of a cache row
+    static constexpr int n = 16 / (int)sizeof(E);
+    uint4 raw;
+    __device__ __forceinline__ float at(int i) const { return to_f32(reinterpret_cast<const E *>(&raw)[i]); }
+};
+
+// SPLIT false: warp w of the CTA owns token blockIdx.x * 8 + w, all of its keys.  SPLIT true: the CTA owns token blockIdx.x
+// and warp w takes the key tiles w, w + 8, ...
+template <typename E, bool SPLIT>
+__global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
+                                                                  const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
+                                                                  int64_t T, int H, int G, int D, int Dv, int64_t window,
+                                                                  const float *__restrict__ cs_v, E *__restrict__ out, int vec) {
+    extern __shared__ __align__(16) float wa_smem[]; // q: [kWarps][Dp]; merge: [kWarps][2 + 64 * kMaxDvRegs / 2 ...]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y, g = h / (H / G);
+    const int Dp = (D + 3) & ~3;
+    const int64_t t = SPLIT ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp;
+    const bool active = t < T;
+    float *sq = wa_smem + warp * Dp;
+    if (active)
+        for (int d = lane; d < Dp; d += 32) sq[d] = d < D ? q[(t * H + h) * D + d] : 0.f;
+    __syncwarp();
+    const int64_t i = (int64_t)*pos0 + (active ? t : 0);
+    const int64_t jlo = window > 0 ? max((int64_t)0, i - window + 1) : 0;
+    const int nreg = (Dv + 63) / 64; // pairs of coordinates per lane: c = 2 * lane + 64 * r
+    float acc[kMaxDvRegs];
+#pragma unroll
+    for (int r = 0; r < kMaxDvRegs; r++) acc[r] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
+    if (active) {
+        const int64_t step = SPLIT ? 32 * kWarps : 32;
+        for (int64_t j0 = jlo + (SPLIT ? 32 * warp : 0); j0 <= i; j0 += step) {
+            const int64_t j = j0 + lane;
+            float s = -INFINITY;
+            if (j <= i) {
+                const E *kr = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld + koff;
+                float a0 = 0.f, a1 = 0.f;
+                if (vec) {
+                    constexpr int VN = RowVec<E>::n;
+                    for (int d = 0; d < D; d += VN) {
+                        RowVec<E> kv;
+                        kv.raw = *reinterpret_cast<const uint4 *>(kr + d);
+#pragma unroll
+                        for (int u = 0; u < VN; u += 2) {
+                            a0 = fmaf(kv.at(u), sq[d + u], a0);
+                            a1 = fmaf(kv.at(u + 1), sq[d + u + 1], a1);
+                        }
+                    }
+                } else {
+                    for (int d = 0; d < D; d++) a0 = fmaf(to_f32(kr[d]), sq[d], a0);
+                }
+                s = a0 + a1;
+            }
+            const float m_new = fmaxf(m, warp_max_f32(s)); // finite: key j0 of the tile is always visible
+            const float p = j <= i ? expf(s - m_new) : 0.f;
+            const float corr = expf(m - m_new);            // m = -inf at the first tile: 0
+            l = l * corr + warp_sum_f32(p);
+#pragma unroll
+            for (int r = 0; r < kMaxDvRegs; r++) acc[r] *= corr;
+            m = m_new;
+            const int n_keys = (int)min((int64_t)32, i - j0 + 1);
+            for (int jj = 0; jj < n_keys; jj++) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const int64_t jr = j0 + jj;
+                const E *vr = cache + ((int64_t)table[jr / B] * B + jr % B) * cache_ld + voff;
+#pragma unroll
+                for (int r = 0; r < kMaxDvRegs / 2; r++) {
+                    const int c = 2 * lane + 64 * r;
+                    if (r < nreg && c < Dv) {
+                        acc[2 * r] = fmaf(pj, to_f32(vr[c]), acc[2 * r]);
+                        acc[2 * r + 1] = fmaf(pj, to_f32(vr[c + 1]), acc[2 * r + 1]);
+                    }
+                }
+            }
+        }
+    }
+    if (SPLIT) { // merge the warps' parts: [m, l, acc...] per warp
+        __syncthreads();
+        float *part = wa_smem + kWarps * Dp;
+        const int pw = 2 + 32 * kMaxDvRegs;
+        if (lane == 0) {
+            part[warp * pw] = m;
+            part[warp * pw + 1] = l;
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs; r++) part[warp * pw + 2 + r * 32 + lane] = acc[r];
+        __syncthreads();
+        if (warp != 0) return;
+        float M = -INFINITY;
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, part[w * pw]);
+        l = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs; r++) acc[r] = 0.f;
+        for (int w = 0; w < kWarps; w++) {
+            const float mw = part[w * pw];
+            if (mw == -INFINITY) continue; // a warp without keys
+            const float f = expf(mw - M);
+            l = fmaf(part[w * pw + 1], f, l);
+#pragma unroll
+            for (int r = 0; r < kMaxDvRegs; r++) acc[r] = fmaf(part[w * pw + 2 + r * 32 + lane], f, acc[r]);
+        }
+    }
+    if (!active) return;
+    const float inv = 1.0f / l;
+    const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
+#pragma unroll
+    for (int r = 0; r < kMaxDvRegs / 2; r++) {
+        const int c = 2 * lane + 64 * r;
+        if (r < nreg && c < Dv) {
+            float u = acc[2 * r] * inv, w = acc[2 * r + 1] * inv;
+            if (cv) { // turned back: by -i
+                const float cs = cv[c], sn = cv[c + 1];
+                const float u2 = u * cs + w * sn, w2 = w * cs - u * sn;
+                u = u2;
+                w = w2;
+            }
+            out[(t * H + h) * Dv + c] = from_f32<E>(u);
+            out[(t * H + h) * Dv + c + 1] = from_f32<E>(w);
+        }
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+int64_t ggb_window_cache_ld(int G, int D, int Dv) { return (((int64_t)G * (D + Dv)) + 7) / 8 * 8; }
+
+int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
+                            const float *qn_w, const float *kn_w, float eps, int rot_dims, const float *cos_sin_k, const float *cos_sin_v,
+                            float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache, float *q_out) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "window_qkv_store: dtype %d is neither bf16 nor f32", dt);
+    GGB_CHECK_ARG(q && k && v && pos0 && block_table && cache && q_out && T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0,
+                  "window_qkv_store: bad arguments");
+    GGB_CHECK_ARG(D > 0 && D % 2 == 0 && Dv > 0 && Dv % 2 == 0 && rot_dims >= 0 && rot_dims <= D && rot_dims % 2 == 0 && (!rot_dims || cos_sin_k),
+                  "window_qkv_store: head sizes %d / %d and %d rotated dimensions must be even", D, Dv, rot_dims);
+    const int64_t cld = ggb_window_cache_ld(G, D, Dv);
+    if (dt == GGB_TYPE_BF16)
+        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims,
+                                                                            rot_dims ? cos_sin_k : nullptr, cos_sin_v, scale, pos0, block_table,
+                                                                            block_size, (__nv_bfloat16 *)cache, cld, q_out);
+    else
+        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims,
+                                                                            rot_dims ? cos_sin_k : nullptr, cos_sin_v, scale, pos0, block_table,
+                                                                            block_size, (float *)cache, cld, q_out);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
+                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "window_attn: dtype %d is neither bf16 nor f32", dt);
+    GGB_CHECK_ARG(q && cache && block_table && pos0 && out && T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && D > 0 && Dv > 0 &&
+                      Dv % 2 == 0 && Dv <= 32 * kMaxDvRegs,
+                  "window_attn: bad arguments (value size %d, even and at most %d)", Dv, 32 * kMaxDvRegs);
+    const int64_t cld = ggb_window_cache_ld(G, D, Dv);
+    const int Dp = (D + 3) & ~3;
+    const int es = dt == GGB_TYPE_BF16 ? 2 : 4, vn = 16 / es;
+    const int vec = D % vn == 0 && ((uintptr_t)cache % 16 == 0); // rows are 8 numbers apart at least: 16-byte aligned in both types
+    const bool split = T < 4 * kWarps;
+    const size_t smem = (size_t)kWarps * Dp * 4 + (split ? (size_t)kWarps * (2 + 32 * kMaxDvRegs) * 4 : 0);
+    GGB_CHECK_ARG(smem <= 48 * 1024, "window_attn: key size %d does not fit shared memory", D);
+    cudaStream_t st = ggb_cuda_stream();
+#define WA_LAUNCH(ET)                                                                                                                       \
+    if (split)                                                                                                                              \
+        window_attn_kernel<ET, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table,      \
+                                                                                                block_size, pos0, T, H, G, D, Dv, window,   \
+                                                                                                cos_sin_v, (ET *)out, vec);                 \
+    else                                                                                                                                    \
+        window_attn_kernel<ET, false><<<dim3((unsigned)((T + kWarps - 1) / kWarps), (unsigned)H), 32 * kWarps, smem, st>>>(                  \
+            q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (ET *)out, vec);
+    if (dt == GGB_TYPE_BF16) { WA_LAUNCH(__nv_bfloat16) } else { WA_LAUNCH(float) }
+#undef WA_LAUNCH
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

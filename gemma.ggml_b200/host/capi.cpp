@@ -181,30 +181,18 @@ int lm_engine_stats(void *e, int64_t *out) {
     out[1] = g->cache()->free_pages();
     out[2] = g->cache()->n_pages();
     out[3] = g->cache()->page_size();
-    safolorn_model *sf = dynamic_cast<safolorn_model *>(g->model());
-    out[4] = sf ? sf->kernels_last_forward() : 0;
-    out[5] = sf ? (int64_t)sf->weight_bytes() : 0;
+    out[4] = g->model()->kernels_last_forward();
+    out[5] = (int64_t)g->model()->weight_bytes();
     return 0;
 }
 int64_t lm_engine_seq_len(void *e, const char *id) { return ((lm_engine *)e)->seq_len(id); }
 // pages of a live sequence (host copy): returns their number, fills at most cap
 int lm_engine_seq_pages(void *e, const char *id, int32_t *out, int cap) { return ((lm_engine *)e)->seq_pages(id, out, cap); }
-int lm_engine_capture(void *e, int on) {
-    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
-    if (!sf) return -1;
-    sf->set_capture(on != 0);
-    return 0;
-}
-int lm_engine_use_graphs(void *e, int on) {
-    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
-    if (!sf) return -1;
-    sf->set_use_graphs(on != 0);
-    return 0;
-}
-int lm_engine_get_capture(void *e, int layer, float *host, int64_t n) {
-    safolorn_model *sf = dynamic_cast<safolorn_model *>(((lm_engine *)e)->model());
-    return sf ? sf->get_capture(layer, host, n) : -1;
-}
+int lm_engine_capture(void *e, int on) { return ((lm_engine *)e)->model()->set_capture(on != 0); }
+int lm_engine_use_graphs(void *e, int on) { return ((lm_engine *)e)->model()->set_use_graphs(on != 0); }
+int lm_engine_get_capture(void *e, int layer, float *host, int64_t n) { return ((lm_engine *)e)->model()->get_capture(layer, host, n); }
+// pages a live sequence holds now (trimmed ones not counted); -1: no such sequence
+int lm_engine_seq_live_pages(void *e, const char *id) { return ((lm_engine *)e)->seq_live_pages(id); }
 // host only: parses a Safolorn configuration text; out[5] = {layers, caching layers, vocab, width, side dim}; -1 and
 // gm_last_error() when the configuration is refused
 int sf_config_probe(const char *text, int64_t *out) {

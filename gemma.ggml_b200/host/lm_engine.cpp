@@ -8,7 +8,7 @@
 int lm_engine::init(lm_model *model, int64_t max_tokens, int page_size, int max_seqs) {
     model_.reset(model);
     if (model->max_live_sequences() > 0) max_seqs = std::min(max_seqs, model->max_live_sequences());
-    int rc = cache_.init(model->dtype(), model->cache_row_elems(), max_tokens, page_size, max_seqs);
+    int rc = cache_.init(model->dtype(), model->cache_row_elems(), max_tokens, page_size, max_seqs, model->state_elems());
     if (rc) {
         err_ = cache_.error();
         return rc;
@@ -40,7 +40,7 @@ int lm_engine::run_entry(const lm_entry &e, std::vector<float> *logits, int32_t 
         seq s;
         s.slot = cache_.open_seq();
         if (s.slot < 0) {
-            err_ = "no free sequence slot for '" + e.id + "'";
+            err_ = "no free sequence slot for '" + e.id + "' (or its state could not be cleared)";
             return GGB_ERR_ARG;
         }
         it = seqs_.emplace(e.id, s).first;
@@ -73,6 +73,7 @@ int lm_engine::run_entry(const lm_entry &e, std::vector<float> *logits, int32_t 
         p.T = (int)(hi - lo);
         p.pos0 = s.len + lo;
         p.block_table_dev = cache_.table_dev(s.slot);
+        p.state_dev = cache_.state(s.slot);
         int rc = model_->forward(p, rows.data(), (int)rows.size());
         if (rc) {
             err_ = model_->last_error();
@@ -97,7 +98,14 @@ int lm_engine::run_entry(const lm_entry &e, std::vector<float> *logits, int32_t 
         }
     }
     s.len += n;
+    // rows no later token can see: their pages serve other sequences from now on
+    if (model_->cache_lookback() > 0) cache_.trim(s.slot, s.len - model_->cache_lookback() + 1);
     return 0;
+}
+
+int lm_engine::seq_live_pages(const std::string &id) const {
+    auto it = seqs_.find(id);
+    return it == seqs_.end() ? -1 : cache_.live_pages(it->second.slot);
 }
 
 int lm_engine::step(const std::vector<lm_entry> &entries, const std::vector<std::string> &end, std::vector<float> *logits) {

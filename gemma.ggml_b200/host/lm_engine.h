@@ -28,6 +28,7 @@ class lm_engine {
     int generate(const std::string &id, const std::vector<int32_t> &prompt, int n_new, std::vector<int32_t> *out);
     int64_t seq_len(const std::string &id) const;
     int seq_pages(const std::string &id, int32_t *out, int cap) const; // pages of a live sequence; returns how many
+    int seq_live_pages(const std::string &id) const; // pages held now (after trimming); -1: no such sequence
     int live_seqs() const { return (int)seqs_.size(); }
     lm_model *model() const { return model_.get(); }
     paged_cache *cache() { return &cache_; }

@@ -18,6 +18,7 @@ struct lm_portion {
     int T = 0;
     int64_t pos0 = 0;
     const int32_t *block_table_dev = nullptr; // device int32 [pages of the sequence]
+    float *state_dev = nullptr;               // the sequence's state block (state_elems() fp32 numbers), or null
 };
 
 class lm_model {
@@ -30,6 +31,12 @@ class lm_model {
     virtual std::vector<int64_t> cache_row_elems() const = 0;
     // called once, before the first forward: the cache the model reads and writes, and the longest sequence it will see
     virtual int bind_cache(paged_cache *cache, int64_t max_positions) = 0;
+    // fp32 numbers of state a sequence carries beside its cache rows (recurrent state, convolution tails, the previous
+    // token); the cache keeps one zero-initialised block per sequence slot and hands it to forward()
+    virtual int64_t state_elems() const { return 0; }
+    // how many positions back the farthest-looking caching layer reads (0: unbounded): the engine gives back the pages
+    // before that while the sequence lives
+    virtual int64_t cache_lookback() const { return 0; }
     virtual int max_live_sequences() const { return 0; } // 0: as many as the engine has slots
     virtual int max_portion() const = 0; // most tokens one forward call takes; the engine cuts longer portions
     // runs the portion from the state earlier portions left in the cache; the logits of rows want[0 .. n_want) of the
@@ -37,6 +44,13 @@ class lm_model {
     virtual int forward(const lm_portion &p, const int32_t *want, int n_want) = 0;
     virtual const float *logits_dev() const = 0;
     virtual std::string last_error() const = 0;
+    // introspection, optional: the residual stream after every layer of the last portion (fp32 [layers][T][width]),
+    // one-token steps as replayed CUDA graphs or eager launches, launch count of the last forward, bytes of weights
+    virtual int set_capture(bool) { return -1; }
+    virtual int get_capture(int /*layer*/, float * /*host*/, int64_t /*n*/) const { return -1; }
+    virtual int set_use_graphs(bool) { return -1; }
+    virtual int kernels_last_forward() const { return 0; }
+    virtual size_t weight_bytes() const { return 0; }
 };
 
 struct lm_load_options {

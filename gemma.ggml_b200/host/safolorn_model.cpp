@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "lm_weights.h"
 #include "seq_cache.h"
 
 // an operator under the library's cudaEvent probes (ggb_prof_*), keyed by operator class like the Gemma path
@@ -29,12 +30,6 @@ int safolorn_model::fail(int rc, const std::string &what) {
 }
 
 // ------------------------------------------------------------------------------------------------ configuration
-std::string sf_rot::key() const {
-    char b[256];
-    snprintf(b, sizeof b, "%d|%.17g|%d|%.17g|%.17g|%.17g|%.17g", dims, base, (int)scaled, factor, original, fast, slow);
-    return b;
-}
-
 int sf_parse_config(const json_value &j, sf_config *c, std::string *err) {
     auto bad = [&](const std::string &m) {
         if (err) *err = "config.json: " + m;
@@ -104,64 +99,7 @@ int sf_parse_config(const json_value &j, sf_config *c, std::string *err) {
     return 0;
 }
 
-// cos / sin of every position, magnitude factor applied: [n_pos][dims / 2][2].  Angles in double on the host.
-static std::vector<float> rot_table(const sf_rot &r, int64_t n_pos) {
-    const int half = r.dims / 2;
-    std::vector<double> f((size_t)half);
-    double mag = 1.0;
-    for (int i = 0; i < half; i++) f[(size_t)i] = std::pow(r.base, -2.0 * i / r.dims);
-    if (r.scaled) {
-        const double two_pi = 6.283185307179586476925286766559;
-        auto corr = [&](double t) { return r.dims * std::log(r.original / (two_pi * t)) / (2.0 * std::log(r.base)); };
-        const double lo = std::max(std::floor(corr(r.fast)), 0.0), hi = std::min(std::ceil(corr(r.slow)), (double)r.dims - 1.0);
-        for (int i = 0; i < half; i++) {
-            const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
-            f[(size_t)i] = f[(size_t)i] / r.factor * ramp + f[(size_t)i] * (1.0 - ramp);
-        }
-        mag = 0.1 * std::log(r.factor) + 1.0;
-    }
-    std::vector<float> t((size_t)n_pos * (size_t)half * 2);
-    for (int64_t p = 0; p < n_pos; p++)
-        for (int i = 0; i < half; i++) {
-            const double a = (double)p * f[(size_t)i];
-            t[((size_t)p * half + i) * 2] = (float)(std::cos(a) * mag);
-            t[((size_t)p * half + i) * 2 + 1] = (float)(std::sin(a) * mag);
-        }
-    return t;
-}
-
 // ------------------------------------------------------------------------------------------------ weights
-static inline float bf16_to_f32(uint16_t h) {
-    uint32_t u = (uint32_t)h << 16;
-    float f;
-    memcpy(&f, &u, 4);
-    return f;
-}
-static inline uint16_t f32_to_bf16(float f) { // round to nearest even
-    uint32_t u;
-    memcpy(&u, &f, 4);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
-    u += 0x7fffu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
-}
-
-static int tensor_f32(const st_tensor &t, std::vector<float> *out) {
-    const size_t n = (size_t)t.numel();
-    out->resize(n);
-    if (t.dtype == "BF16") {
-        for (size_t i = 0; i < n; i++) {
-            uint16_t h;
-            memcpy(&h, t.data + 2 * i, 2);
-            (*out)[i] = bf16_to_f32(h);
-        }
-    } else if (t.dtype == "F32") {
-        memcpy(out->data(), t.data, n * 4);
-    } else {
-        return -1;
-    }
-    return 0;
-}
-
 int safolorn_model::upload_matrix(const std::vector<float> &host, void **dev) {
     const size_t n = host.size();
     void *d = nullptr;
@@ -191,55 +129,6 @@ int safolorn_model::upload_f32(const std::vector<float> &host, float **dev) {
     *dev = (float *)d;
     return 0;
 }
-
-namespace {
-// where a layer's numbers come from: the file, or a counter-based generator for throughput runs
-struct weight_source {
-    const safetensors_file *file;
-    uint64_t seed;
-    std::string *err;
-    uint64_t counter = 0;
-    static uint64_t mix(uint64_t x) {
-        x += 0x9E3779B97F4A7C15ull;
-        x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
-        x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
-        return x ^ (x >> 31);
-    }
-    // rows x cols numbers of `name`; random: uniform in +-amp around `mean`
-    int get(const std::string &name, int64_t rows, int64_t cols, float amp, float mean, std::vector<float> *out) {
-        if (file) {
-            const st_tensor *t = file->find(name);
-            if (!t) {
-                *err = "tensor '" + name + "' is missing";
-                return -1;
-            }
-            if (t->numel() != rows * cols) {
-                *err = "tensor '" + name + "' has " + std::to_string(t->numel()) + " numbers, the configuration asks for " +
-                       std::to_string(rows) + " x " + std::to_string(cols);
-                return -1;
-            }
-            if (tensor_f32(*t, out)) {
-                *err = "tensor '" + name + "': type " + t->dtype + " is not read";
-                return -1;
-            }
-            return 0;
-        }
-        const uint64_t key = mix(seed + 0xD1B54A32D192ED03ull * ++counter);
-        out->resize((size_t)(rows * cols));
-        for (size_t i = 0; i < out->size(); i++) {
-            const uint64_t r = mix(key + i);
-            (*out)[i] = mean + amp * (float)((double)(r >> 11) / 9007199254740992.0 * 2.0 - 1.0);
-        }
-        return 0;
-    }
-    // 1 when the tensor holds one number (file), as `dflt` says otherwise
-    int numel(const std::string &name, int dflt) const {
-        if (!file) return dflt;
-        const st_tensor *t = file->find(name);
-        return t ? (int)t->numel() : -1;
-    }
-};
-} // namespace
 
 int safolorn_model::load(const safetensors_file *file, uint64_t seed) {
     const sf_config &c = cfg_;

@@ -14,15 +14,10 @@
 
 #include "ggml_b200.h"
 #include "lm_model.h"
+#include "rotary.h"
 #include "safetensors.h"
 
-struct sf_rot { // rotary positions of a mixer
-    int dims = 0;
-    double base = 10000.0;
-    bool scaled = false;
-    double factor = 1.0, original = 0.0, fast = 0.0, slow = 0.0;
-    std::string key() const;
-};
+typedef rot_spec sf_rot; // rotary positions of a mixer (rotary.h)
 
 struct sf_layer_cfg {
     // mixer
@@ -79,11 +74,17 @@ class safolorn_model : public lm_model {
 
     const sf_config &config() const { return cfg_; }
     // keep the residual stream after every layer of the next forward calls (fp32 [layers][T][width] of the last portion)
-    void set_capture(bool on) { capture_ = on; }
-    void set_use_graphs(bool on) { use_graphs_ = on; }
-    int get_capture(int layer, float *host, int64_t n) const;
-    size_t weight_bytes() const { return weight_bytes_; }
-    int kernels_last_forward() const { return kernels_last_; }
+    int set_capture(bool on) override {
+        capture_ = on;
+        return 0;
+    }
+    int set_use_graphs(bool on) override {
+        use_graphs_ = on;
+        return 0;
+    }
+    int get_capture(int layer, float *host, int64_t n) const override;
+    size_t weight_bytes() const override { return weight_bytes_; }
+    int kernels_last_forward() const override { return kernels_last_; }
 
   private:
     safolorn_model() {}

@@ -1,14 +1,17 @@
 // seq_cache.cpp — see seq_cache.h
 #include "seq_cache.h"
 
+#include <algorithm>
+
 #include "ggml_b200.h"
 
 paged_cache::~paged_cache() {
     for (void *p : layers_) ggb_buffer_free(p);
     if (tables_dev_) ggb_buffer_free(tables_dev_);
+    if (state_) ggb_buffer_free(state_);
 }
 
-int paged_cache::init(int dt, const std::vector<int64_t> &row_elems, int64_t max_tokens, int page_size, int max_seqs) {
+int paged_cache::init(int dt, const std::vector<int64_t> &row_elems, int64_t max_tokens, int page_size, int max_seqs, int64_t state_elems) {
     if (page_size <= 0 || max_tokens <= 0 || max_seqs <= 0 || !ggb_dtype_size(dt)) {
         err_ = "paged_cache: bad sizes";
         return GGB_ERR_ARG;
@@ -31,6 +34,10 @@ int paged_cache::init(int dt, const std::vector<int64_t> &row_elems, int64_t max
         if ((rc = ggb_buffer_memset(d, 0, bytes))) return rc;
     }
     int rc = ggb_buffer_alloc((size_t)max_seqs * (size_t)n_pages_ * 4, (void **)&tables_dev_);
+    if (!rc && state_elems > 0) {
+        state_elems_ = (state_elems + 3) / 4 * 4; // blocks stay 16-byte aligned
+        rc = ggb_buffer_alloc((size_t)max_seqs * (size_t)state_elems_ * 4, (void **)&state_);
+    }
     if (rc) err_ = ggb_last_error();
     return rc;
 }
@@ -40,6 +47,8 @@ int paged_cache::open_seq() {
         if (!seqs_[i].open) {
             seqs_[i].open = true;
             seqs_[i].pages.clear();
+            seqs_[i].trimmed = 0;
+            if (state_ && ggb_buffer_memset(state((int)i), 0, (size_t)state_elems_ * 4)) return -1; // stream-ordered: before the first step
             return (int)i;
         }
     return -1;
@@ -63,7 +72,25 @@ int paged_cache::reserve(int slot, int64_t n_tokens) {
 
 void paged_cache::close_seq(int slot) {
     seq &s = seqs_[(size_t)slot];
-    for (size_t i = s.pages.size(); i-- > 0;) free_.push_back(s.pages[i]); // the first page is reused first
+    for (size_t i = s.pages.size(); i-- > 0;)
+        if (s.pages[i] >= 0) free_.push_back(s.pages[i]); // the first page is reused first
     s.pages.clear();
+    s.trimmed = 0;
     s.open = false;
+}
+
+void paged_cache::trim(int slot, int64_t first_needed) {
+    seq &s = seqs_[(size_t)slot];
+    if (first_needed <= 0) return;
+    const size_t keep_from = std::min((size_t)(first_needed / page_), s.pages.size());
+    for (size_t i = s.trimmed; i < keep_from; i++) {
+        free_.push_back(s.pages[i]);
+        s.pages[i] = -1;
+    }
+    if (keep_from > s.trimmed) s.trimmed = keep_from;
+}
+
+int paged_cache::live_pages(int slot) const {
+    const seq &s = seqs_[(size_t)slot];
+    return (int)(s.pages.size() - s.trimmed);
 }

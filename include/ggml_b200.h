@@ -272,6 +272,64 @@ int ggb_op_residual_side(int dt, float *x, const float *a, const float *f, int64
                          int64_t e_ld, int64_t e_off, int sd, const void *w_gate, const void *w_proj, const float *nw, float eps);
 int ggb_op_cvt_bf16_f32(const void *x_bf16, int64_t n, float *y);
 
+/* token embedding with a hashed bigram table: y[t] = table[ids[t]] + bigram[row_t], row_t = (prev_t * mul_prev +
+ * ids[t] * mul_cur) mod buckets with prev_t = ids[t - 1] and, for t = 0, the sequence's carried *prev_state; the first
+ * token of a sequence (*pos0 + t == 0) takes row `buckets` (the table has buckets + 1 rows).  *prev_state <- ids[T - 1]. */
+int ggb_op_embed_bigram(int dt, const void *table, const void *bigram, const int32_t *ids, int64_t T, int64_t E, int64_t buckets,
+                        int64_t mul_prev, int64_t mul_cur, const int32_t *pos0, int32_t *prev_state, float *y);
+/* v = sa a (+ sb b) (+ bias); n = v cut into `groups` equal consecutive parts, each divided by its own
+ * sqrt(mean(part^2) + eps), times w.  With x (fp32): x += n and y (dt, may be NULL) = the new x; without x: y = n. */
+int ggb_op_group_norm_add(int dt, const float *a, float sa, const float *b, float sb, const float *bias, const float *w, int groups,
+                          float eps, int64_t E, int64_t T, float *x, void *y);
+/* gu rows = [gate F | up F] (fp32): y = act(gate + bg) * (up + bu); biases may be NULL; act 0: relu, 1: silu, 2: gelu_tanh */
+int ggb_op_glu_bias(int dt, const float *gu, int64_t F, int64_t T, const float *bg, const float *bu, int act, void *y);
+/* x <- cap * tanh(x / cap) */
+int ggb_op_softcap(float *x, int64_t n, float cap);
+/* o rows = [n_groups][gs] fp32 (row stride ldo): y = o / sqrt(mean over the group (o^2) + eps) * w[i %% w_period] *
+ * act(gate) with gate fp32 rows of stride ldg; act 0: sigmoid, 1: silu; y in dt, dense [T][n_groups * gs] */
+int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int64_t ldg, int64_t T, int n_groups, int gs, const float *w,
+                     int w_period, float eps, int act, void *y);
+
+/* ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
+ * State that a sequence carries from token to token (fp32, one block per sequence, handed in by the caller): tails of
+ * causal convolutions and the matrices S [heads][D][Dv] of linear-attention recurrences.
+ *
+ * causal convolution over time on each channel: with xx = tail (the taps - 1 inputs before this portion; zeros at a
+ * sequence's start) followed by x, y[t][c] = (add_input ? x[t][c] : 0) + sum_j w[c][j] xx[t + j][c] (the last tap weighs
+ * the current token); act 1: y = silu(y).  y is fp32 (y_f32, row stride ldy) and / or dt (y_dt, dense [T][C]).  tail
+ * [(taps - 1)][C] is replaced by the last taps - 1 inputs.  taps <= 8. */
+int ggb_op_causal_conv(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, int taps, int add_input, int act,
+                       float *tail, float *y_f32, int64_t ldy, void *y_dt);
+/* lightning attention: q, k [T][H * D], v [T][H * Dv] raw projections (row stride ld); per head with q = silu(q),
+ * k = silu(k), v = silu(v): S <- decay[h] S + k v^T, o = S^T q.  state [H][D][Dv] in / out, o fp32 [T][H * Dv]. */
+int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int D, int Dv, const float *decay,
+                          float *state, float *o, int64_t ldo);
+/* gated delta rule: q, k [T][G * D] and v [T][H * Dv] (after their convolutions and activations; row stride ld), b, a
+ * [T][H] raw projections (row stride ld_ba); head h uses q / k head h / (H / G).  qn = q / sqrt(sum q^2 + 1e-6) * D^(-1/2),
+ * kn = k / sqrt(sum k^2 + 1e-6), beta = sigmoid(b), g = exp(-exp(A_log[h]) softplus(a + dt_bias[h]));
+ * S <- g S; u = beta (v - S^T kn); S <- S + kn u^T; o = S^T qn.  state [H][D][Dv] in / out, o fp32 [T][H * Dv]. */
+int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, const float *a, int64_t ld_ba, int64_t T,
+                       int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo);
+
+/* ------------------------------------------------------------------ sliding-window attention (csrc/window_attention.cu)
+ * Grouped-query soft-max attention over a paged cache whose row per position is [k (G * D) | v (G * Dv)] in dt,
+ * ggb_window_cache_ld numbers apart (pages as in the latent cache).  Values are stored rotated by their own position
+ * (pairs (2m, 2m + 1) over all Dv, table cos_sin_v) and a head's output is turned back by the reader's position.
+ * cos_sin tables: [positions][pairs][2] fp32.
+ *
+ * qkv_store: q [T][H * D], k [T][G * D], v [T][G * Dv] raw projections (row stride ld).  With qn_w / kn_w the whole q / k
+ * row is divided by its root mean square and multiplied by that weight first.  Pairs (2i, 2i + 1), 2i < rot_dims, of every
+ * head of q and k are turned by the position (cos_sin_k); q times scale -> q_out fp32 [T][H * D]; k and v (cos_sin_v may
+ * be NULL: stored as they are) -> the cache row of position *pos0 + t. */
+int64_t ggb_window_cache_ld(int G, int D, int Dv);
+int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
+                            const float *qn_w, const float *kn_w, float eps, int rot_dims, const float *cos_sin_k, const float *cos_sin_v,
+                            float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache, float *q_out);
+/* token t at position i = *pos0 + t sees the keys j with 0 <= i - j < window (window <= 0: every j <= i); query head h
+ * reads key / value head h / (H / G); out (dt) [T][H * Dv] */
+int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
+                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out);
+
 /* ------------------------------------------------------------------ latent attention (csrc/latent_attention.cu)
  * The cache of a layer holds one row [c (R) | kr (Dr)] per position, ggb_latent_cache_ld(R, Dr) numbers apart, in pages
  * of block_size positions: position j is row block_table[j / block_size] * block_size + j %% block_size.  The step's
