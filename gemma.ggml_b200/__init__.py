@@ -140,6 +140,17 @@ _CUDA_SIG = {
     "ggb_latent_attn_scratch_bytes": (sz, [i64, i32, i32, i32]),
     "ggb_op_latent_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, vp]),
     "ggb_op_latent_attn_out": (i32, [i32, vp, i32, vp, vp, i64, i32, i32, i32, vp]),
+    "ggb_op_embed_bigram": (i32, [i32, vp, vp, vp, i64, i64, i64, i64, i64, vp, vp, vp]),
+    "ggb_op_group_norm_add": (i32, [i32, vp, f32, vp, f32, vp, vp, i32, f32, i64, i64, vp, vp]),
+    "ggb_op_glu_bias": (i32, [i32, vp, i64, i64, vp, vp, i32, vp]),
+    "ggb_op_softcap": (i32, [vp, i64, f32]),
+    "ggb_op_norm_gate": (i32, [i32, vp, i64, vp, i64, i64, i32, i32, vp, i32, f32, i32, vp]),
+    "ggb_op_causal_conv": (i32, [i32, vp, i64, i64, i64, vp, i32, i32, i32, vp, vp, i64, vp]),
+    "ggb_op_lightning_attn": (i32, [vp, vp, vp, i64, i64, i32, i32, i32, vp, vp, vp, i64]),
+    "ggb_op_gated_delta": (i32, [vp, vp, vp, i64, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, i64]),
+    "ggb_window_cache_ld": (i64, [i32, i32, i32]),
+    "ggb_op_window_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, f32, i32, vp, vp, f32, vp, vp, i32, vp, vp]),
+    "ggb_op_window_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp]),
     "ggb_op_moe_route": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp, vp]),
     "ggb_moe_max_tiles": (i32, [i64, i32]), "ggb_moe_group_ints": (sz, [i64, i32]),
     "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),
@@ -180,8 +191,10 @@ _HOST_SIG = {
     "lm_engine_stats": (i32, [vp, P(i64)]), "lm_engine_seq_len": (i64, [vp, C.c_char_p]),
     "lm_engine_seq_pages": (i32, [vp, C.c_char_p, vp, i32]),
     "lm_engine_capture": (i32, [vp, i32]), "lm_engine_use_graphs": (i32, [vp, i32]), "lm_engine_get_capture": (i32, [vp, i32, vp, i64]),
+    "lm_engine_seq_live_pages": (i32, [vp, C.c_char_p]),
     "lm_architectures_csv": (i32, [C.c_char_p, i32]),
     "sf_config_probe": (i32, [C.c_char_p, P(i64)]),
+    "bg_config_probe": (i32, [C.c_char_p, P(i64)]),
     "st_probe": (i32, [C.c_char_p, C.c_char_p, P(i64), P(i64), C.c_char_p, i32, P(i64)]),
     "mul_mat": (None, [i64, i64, i64, i64, i64, i64, i64, sz, i64, vp, vp, vp, vp, i32, vp]),
     "init_cuda_offload": (i32, [i32]),
@@ -716,6 +729,10 @@ class Engine:
         buf = np.empty(self.stats()["pages"], dtype=np.int32)
         n = host_lib().lm_engine_seq_pages(self.h, str(seq_id).encode(), _ptr(buf), len(buf))
         return buf[:max(n, 0)].copy()
+
+    def seq_live_pages(self, seq_id):
+        """pages the sequence holds now: pages behind every window of a windowed model have gone back to the pool"""
+        return int(host_lib().lm_engine_seq_live_pages(self.h, str(seq_id).encode()))
 
     def capture(self, on=True):
         self._check(host_lib().lm_engine_capture(self.h, 1 if on else 0), "capture")

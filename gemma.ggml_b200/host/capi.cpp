@@ -8,6 +8,7 @@
 #include "gemma_model.h"
 #include "gguf_loader.h"
 #include "lm_engine.h"
+#include "begupel_model.h"
 #include "safolorn_model.h"
 #include "tensor_dump.h"
 
@@ -203,6 +204,18 @@ int sf_config_probe(const char *text, int64_t *out) {
     int64_t own = 0;
     for (const auto &l : c.layers) own += l.kv_from < 0;
     out[0] = (int64_t)c.layers.size(); out[1] = own; out[2] = c.vocab; out[3] = c.width; out[4] = c.side_dim;
+    return 0;
+}
+// host only: parses a Begupel configuration text; out[6] = {layers, layers with a window cache, vocab, width, norm groups,
+// taps of the input convolution}; -1 and gm_last_error() when the configuration is refused
+int bg_config_probe(const char *text, int64_t *out) {
+    json_value j;
+    bg_config c;
+    if (!json_parser(text, strlen(text)).parse(&j, &g_capi_err)) return -1;
+    if (bg_parse_config(j, &c, &g_capi_err)) return -1;
+    int64_t win = 0;
+    for (const auto &l : c.layers) win += l.type == 1;
+    out[0] = (int64_t)c.layers.size(); out[1] = win; out[2] = c.vocab; out[3] = c.width; out[4] = c.groups; out[5] = c.taps;
     return 0;
 }
 // host only: a tensor of a .safetensors file: returns its number of dimensions (shape[0 .. 8) filled, *nbytes, dtype text),
