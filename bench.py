@@ -733,11 +733,164 @@ def run_safolorn(args):
                       "peaks": peaks, "sizes": records}), flush=True)
 
 
+BEGUPEL_SIZES = {  # width, layers, heads, kv heads, head size, window, delta heads, delta kv heads, lightning heads, ff, vocab
+    "s": (1024, 8, 8, 2, 128, 1024, 8, 4, 8, 4096, 32000),
+    "m": (2048, 8, 16, 4, 128, 1024, 16, 8, 16, 8192, 32000),
+    "l": (4096, 4, 32, 8, 128, 2048, 32, 16, 32, 12288, 32000),
+}
+
+
+def begupel_config(size):
+    """Layers alternate: window attention beside a gated delta rule, then lightning attention; each with a dense feed-forward."""
+    W, L, H, G, D, win, Hr, Gr, Hl, ff, V = BEGUPEL_SIZES[size]
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            mx = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": win},
+                           "rot": {"base": 1000000.0, "dims": D, "scaling": {"factor": 4.0}}},
+                  "right": {"heads": Hr, "kv_heads": Gr, "dim": D, "vdim": D, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}
+            layers.append({"type": "parallel", "mixer": mx, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            mx = {"heads": Hl, "dim": D, "vdim": D, "decay": [float(np.exp(-1.0 / (2.0 * 2.0 ** (10.0 * h / Hl)))) for h in range(Hl)]}
+            layers.append({"type": "lightning", "mixer": mx, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Begupel", "vocab": V, "width": W, "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 4},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 31}}, "logit_softcap": 30.0, "layers": layers}
+
+
+BG_OPS = ("op_linear", "op_attn", "op_attn_prep", "op_attn_out", "op_recurrence", "op_conv", "op_norm", "op_act", "op_residual", "op_rows")
+
+
+def _engine_times(G, eng, V, T, ctx, n_dec, ops):
+    """prefill of T tokens and greedy decode at n_kv ~ ctx through an engine: host-timed seconds, cudaEvent ms per operator class"""
+    L = G.cuda_lib()
+    r = np.random.default_rng(0)
+    prompt = r.integers(0, V, T).astype(np.int32)
+
+    def prefill():
+        eng.step([("p", prompt, [T - 1])], ["p"])
+    for _ in range(3):
+        prefill()
+    reps = 5
+    with ClockSampler(0) as clocks:
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            prefill()
+        pf = (time.perf_counter() - t0) / reps
+    L.ggb_prof_enable(1)
+    G.prof_reset()
+    prefill()
+    G.sync()
+    pf_ops = {k: G.prof_get(k)[0] for k in ops}
+    L.ggb_prof_enable(0)
+    eng.step([("d", r.integers(0, V, ctx - 1).astype(np.int32), [])])
+    eng.generate("d", [1], 8)
+    t0 = time.perf_counter()
+    eng.generate("d", [2], n_dec)
+    dec = (time.perf_counter() - t0) / n_dec
+    kernels = eng.stats()["kernels_last_forward"]
+    eng.use_graphs(False)
+    eng.generate("d", [3], 4)
+    L.ggb_prof_enable(1)
+    G.prof_reset()
+    eng.generate("d", [4], 8)
+    G.sync()
+    dc_ops = {k: G.prof_get(k)[0] / 8 for k in ops}
+    L.ggb_prof_enable(0)
+    eng.end("d")
+    return pf, pf_ops, dec, dc_ops, kernels, clocks.summary()
+
+
+def run_begupel(args):
+    """--arch begupel: prefill and decode throughput of the Begupel design (random bf16 weights) at layer sizes of real
+    models, through the serving engine (host call: H2D token ids, operator launches / graph replay, D2H result), with
+    cudaEvent time per operator class and roofline fractions; beside it Safolorn, the closest model of the framework
+    (same engine, same plain bf16 products), at the same width, depth, heads and feed-forward size, all layers dense."""
+    import gemma_ggml_b200 as G
+    G.init(0)
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks = {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops_sustained": float(pk["bf16_tflops_sustained"]), "source": "MEASURED_PEAKS.json"}
+    except Exception:
+        pass
+    T, ctx, n_dec = args.prefill_tokens if args.prefill_tokens != 512 else 2048, args.ctx, min(args.steps, 128)
+    records = {}
+    for size in args.sizes.split(","):
+        cfg = begupel_config(size)
+        W, nl, H, Gk, D, win, Hr, Gr, Hl, ff, V = BEGUPEL_SIZES[size]
+        eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+        pf, pf_ops, dec, dc_ops, kernels, clocks = _engine_times(G, eng, V, T, ctx, n_dec, BG_OPS)
+        wbytes = eng.stats()["weight_bytes"]
+        eng.close()
+        lin_params = attn_flops = rec_flops = 0.0
+        cache_bytes = state_bytes = 0.0
+        visible = float(sum(min(i + 1, win) for i in range(T)))
+        for Ly in cfg["layers"]:
+            if Ly["type"] == "parallel":
+                lin_params += W * (H * D + 2 * Gk * D) + W * H * D + W * (2 * Gr * D + 2 * Hr * D + 2 * Hr) + W * Hr * D
+                attn_flops += 4.0 * H * D * visible
+                rec_flops += 7.0 * Hr * D * D * T
+                cache_bytes += 2.0 * min(ctx, win) * 2 * Gk * D
+                state_bytes += 8.0 * Hr * D * D
+            else:
+                lin_params += W * 4 * Hl * D + W * Hl * D
+                rec_flops += 4.0 * Hl * D * D * T
+                state_bytes += 8.0 * Hl * D * D
+            lin_params += 3.0 * ff * W
+        lin_flops = 2.0 * T * lin_params + 2.0 * V * W
+        lin_bytes = 2.0 * (lin_params + V * W)
+        rec = {
+            "config": {"width": W, "layers": nl, "heads": H, "kv_heads": Gk, "dim": D, "window": win, "delta_heads": Hr, "delta_kv_heads": Gr,
+                       "lightning_heads": Hl, "ff": ff, "vocab": V, "weight_bytes": wbytes},
+            "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks,
+                        "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
+                        "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                        "attn_tflops_cuda_cores": attn_flops / (pf_ops["op_attn"] / 1e3) / 1e12,
+                        "recurrence_tflops_cuda_cores": rec_flops / (pf_ops["op_recurrence"] / 1e3) / 1e12},
+            "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
+                       "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                       "attn_gbs": cache_bytes / (dc_ops["op_attn"] / 1e3) / 1e9, "recurrence_gbs": state_bytes / (dc_ops["op_recurrence"] / 1e3) / 1e9,
+                       "token_frac_of_hbm_roofline": ((lin_bytes + cache_bytes + state_bytes) / (peaks["hbm_gbs"] * 1e9)) / dec},
+        }
+        if not args.no_sub_records:  # Safolorn at equal size: latent attention with heads of the same size, dense feed-forward everywhere
+            R = 512 if W >= 2048 else 256
+            mx = {"heads": H, "dim": D, "rot_dim": 64, "vdim": D, "kv_rank": R, "scale": (D + 64) ** -0.5,
+                  "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            scfg = {"architecture": "Safolorn", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+                    "layers": [{"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}} for _ in range(nl)]}
+            seng = G.Engine(config=scfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+            spf, spf_ops, sdec, sdc_ops, skernels, _ = _engine_times(G, seng, V, T, ctx, n_dec, BG_OPS)
+            s_params = nl * (W * (H * (D + 64) + R + 64) + W * H * D + 3.0 * ff * W)
+            s_flops, s_bytes = 2.0 * T * s_params + 2.0 * V * W, 2.0 * (s_params + V * W)
+            s_attn = 2.0 * nl * H * (2 * R + 64) * T * (T + 1) / 2
+            s_cache = 2.0 * nl * ctx * (R + 64)
+            rec["safolorn_equal_size"] = {
+                "config": {"kv_rank": R, "rot_dim": 64, "weight_bytes": seng.stats()["weight_bytes"]},
+                "prefill": {"tokens_per_s": T / spf, "ms": 1e3 * spf, "op_ms": spf_ops, "linear_tflops": s_flops / (spf_ops["op_linear"] / 1e3) / 1e12,
+                            "linear_frac_of_tensor_peak": s_flops / (spf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                            "attn_tflops_cuda_cores": s_attn / (spf_ops["op_attn"] / 1e3) / 1e12},
+                "decode": {"tokens_per_s": 1.0 / sdec, "us_per_token": 1e6 * sdec, "kernels_per_token": skernels, "op_us": {k: 1e3 * v for k, v in sdc_ops.items()},
+                           "linear_gbs": s_bytes / (sdc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": s_bytes / (sdc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                           "attn_gbs": s_cache / (sdc_ops["op_attn"] / 1e3) / 1e9,
+                           "token_frac_of_hbm_roofline": ((s_bytes + s_cache) / (peaks["hbm_gbs"] * 1e9)) / sdec},
+            }
+            seng.close()
+        records[size] = rec
+    first = records[args.sizes.split(",")[0]]
+    print(json.dumps({"metric": "begupel decode tokens/s", "value": first["decode"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": n_dec, "warmup": 8, "ms_per_step": first["decode"]["us_per_token"] / 1e3, "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random bf16 weights of the configured sizes)",
+                      "config": {"workload": "Begupel sizes " + args.sizes + ": prefill of %d tokens, greedy decode at n_kv %d, through the serving engine" % (T, ctx),
+                                 "l2": "weights of every size exceed the 126 MB L2"},
+                      "peaks": peaks, "sizes": records}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn"],
-                    help="gemma: the headline workload (default); safolorn: throughput of the Safolorn design beside Gemma at equal size")
-    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn: which of the sizes s, m, l to run")
+    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn", "begupel"],
+                    help="gemma: the headline workload (default); safolorn: throughput of the Safolorn design beside Gemma at equal size; "
+                         "begupel: throughput of the Begupel design beside Safolorn at equal size")
+    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn / begupel: which of the sizes s, m, l to run")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
@@ -757,6 +910,8 @@ def main():
         run_reference(args)
     elif args.arch == "safolorn":
         run_safolorn(args)
+    elif args.arch == "begupel":
+        run_begupel(args)
     elif args.mode == "prefill":
         run_prefill(args)
     else:
