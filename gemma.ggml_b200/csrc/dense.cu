@@ -542,20 +542,21 @@ __global__ void softcap_kernel(float *x, int64_t n, float cap) {
     if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
-// a warp per (token, group): o / rms(o) * w * act(gate)
-template <typename E>
+// a warp (WIDE: a CTA) per (token, group): o / rms(o) * w * act(gate)
+template <typename E, bool WIDE>
 __global__ void __launch_bounds__(256) norm_gate_kernel(const float *__restrict__ o, int64_t ldo, const float *__restrict__ gate, int64_t ldg,
                                                         int64_t T, int n_groups, int gs, const float *__restrict__ w, int w_period, float eps,
                                                         int act, E *__restrict__ y) {
-    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __shared__ float red[8];
+    const int64_t item = WIDE ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= T * n_groups) return;
     const int64_t t = item / n_groups;
-    const int g = (int)(item - t * n_groups), lane = threadIdx.x & 31;
+    const int g = (int)(item - t * n_groups), lane = WIDE ? threadIdx.x : threadIdx.x & 31, step = WIDE ? 256 : 32;
     const float *orow = o + t * ldo + (int64_t)g * gs, *grow = gate + t * ldg + (int64_t)g * gs;
     float ss = 0.f;
-    for (int i = lane; i < gs; i += 32) ss = fmaf(orow[i], orow[i], ss);
-    const float r = 1.0f / sqrtf(warp_sum_f32(ss) / (float)gs + eps);
-    for (int i = lane; i < gs; i += 32) {
+    for (int i = lane; i < gs; i += step) ss = fmaf(orow[i], orow[i], ss);
+    const float r = 1.0f / sqrtf((WIDE ? block_sum_256(ss, red) : warp_sum_f32(ss)) / (float)gs + eps);
+    for (int i = lane; i < gs; i += step) {
         const float z = grow[i];
         const float s = 1.0f / (1.0f + expf(-z));
         y[(t * n_groups + g) * gs + i] = from_f32<E>(orow[i] * r * w[(g * gs + i) % w_period] * (act == 1 ? z * s : s));
@@ -628,11 +629,13 @@ int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int
     GGB_CHECK_ARG(o && gate && w && y && T > 0 && n_groups > 0 && gs > 0 && w_period > 0 && ldo >= (int64_t)n_groups * gs &&
                       ldg >= (int64_t)n_groups * gs && (act == 0 || act == 1),
                   "norm_gate: bad arguments");
-    const unsigned blocks = (unsigned)((T * n_groups + 7) / 8);
-    if (dt == GGB_TYPE_BF16)
-        norm_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (__nv_bfloat16 *)y);
-    else
-        norm_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (float *)y);
+    const bool wide = gs >= 512; // a long group gets a CTA of its own
+    const unsigned blocks = wide ? (unsigned)(T * n_groups) : (unsigned)((T * n_groups + 7) / 8);
+#define NG_LAUNCH(ET)                                                                                                                          \
+    if (wide) norm_gate_kernel<ET, true><<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (ET *)y); \
+    else norm_gate_kernel<ET, false><<<blocks, 256, 0, ggb_cuda_stream()>>>(o, ldo, gate, ldg, T, n_groups, gs, w, w_period, eps, act, (ET *)y);
+    if (dt == GGB_TYPE_BF16) { NG_LAUNCH(__nv_bfloat16) } else { NG_LAUNCH(float) }
+#undef NG_LAUNCH
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

@@ -5,8 +5,9 @@
 //
 // The two recurrences share one kernel: a CTA owns one head and a slice of CV value columns (columns are independent
 // in both rules), NS lanes share a column and each keeps D / NS numbers of it in registers for the whole portion.
-// Per token the lanes' partial sums meet through two shuffles.  Tokens are staged through shared memory in chunks;
-// the staging pass also does what is per token and parallel: activations, unit norms, decay and step size.
+// Per token the lanes' partial sums meet through two shuffles.  Tokens are staged through shared memory in chunks by
+// four more warps, one chunk ahead of the recurrence; the staging pass also does what is per token and parallel:
+// activations, unit norms, decay and step size.
 //
 // Compiled with -fmad=false: multiply-adds are spelled fmaf().
 #include "common.cuh"
@@ -102,15 +103,87 @@ struct rec_args {
 
 // MODE 0: lightning (q, k, v = silu of the raw rows; S <- decay S + k v^T; o = S^T q)
 // MODE 1: gated delta rule (unit q and k, q * D^-1/2; S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q)
+//
+// 256 threads: threads 0..127 run the recurrence on the chunk in one buffer while warps 4..7 stage the next chunk into
+// the other (global loads of a warp's four tokens in flight together), one barrier per chunk.
+template <int DS>
+struct rec_smem {
+    static constexpr int DP = DS * kNS; // padded D
+    float q[kChunk][DP], k[kChunk][DP];
+    float v[kChunk][kCV], g[kChunk], beta[kChunk];
+};
+
 template <int DS, int MODE>
-__global__ void __launch_bounds__(kCV *kNS) recurrence_kernel(rec_args p) {
-    constexpr int DP = DS * kNS; // padded D
-    __shared__ __align__(16) float sq[kChunk][DP], sk[kChunk][DP];
-    __shared__ float sv[kChunk][kCV], sg[kChunk], sbeta[kChunk];
+__device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, int64_t t0, int n, int h, int hk, int col0, int pw, int lane, float a_rate,
+                                          float dtb, float q_scale) {
+    constexpr int DP = DS * kNS, PL = (DP + 31) / 32, TPW = kChunk / 4; // numbers per lane and row, tokens per producer warp
+    float qv[TPW][PL], kv[TPW][PL], vv[TPW], bb[TPW], aa[TPW];
+#pragma unroll
+    for (int u = 0; u < TPW; u++) {
+        const int tt = pw + 4 * u;
+        const int64_t t = t0 + min(tt, n - 1); // past the chunk's end: the last token again, not stored
+        const float *qr = p.q + t * p.ld + (int64_t)hk * p.D, *kr = p.k + t * p.ld + (int64_t)hk * p.D;
+#pragma unroll
+        for (int i = 0; i < PL; i++) {
+            const int d = lane + 32 * i;
+            qv[u][i] = d < p.D ? qr[d] : 0.f;
+            kv[u][i] = d < p.D ? kr[d] : 0.f;
+        }
+        vv[u] = (lane < kCV && col0 + lane < p.Dv) ? p.v[t * p.ld + (int64_t)h * p.Dv + col0 + lane] : 0.f;
+        if (MODE == 1) {
+            bb[u] = p.b[t * p.ld_ba + h];
+            aa[u] = p.a[t * p.ld_ba + h];
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < TPW; u++) {
+        const int tt = pw + 4 * u;
+        if (tt >= n) continue;
+        float qm = 1.f, km = 1.f;
+        if (MODE == 0) {
+#pragma unroll
+            for (int i = 0; i < PL; i++) {
+                qv[u][i] = silu_f32(qv[u][i]); // silu(0) = 0: the padding stays zero
+                kv[u][i] = silu_f32(kv[u][i]);
+            }
+            vv[u] = silu_f32(vv[u]);
+        } else {
+            float qs = 0.f, ks = 0.f;
+#pragma unroll
+            for (int i = 0; i < PL; i++) {
+                qs = fmaf(qv[u][i], qv[u][i], qs);
+                ks = fmaf(kv[u][i], kv[u][i], ks);
+            }
+            qs = warp_sum_f32(qs);
+            ks = warp_sum_f32(ks);
+            qm = q_scale / sqrtf(qs + 1e-6f);
+            km = 1.0f / sqrtf(ks + 1e-6f);
+            if (lane == 0) {
+                b.beta[tt] = sigmoid_f32(bb[u]);
+                b.g[tt] = expf(-a_rate * softplus_f32(aa[u] + dtb));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PL; i++) {
+            const int d = lane + 32 * i;
+            if (d < DP) {
+                b.q[tt][d] = qv[u][i] * qm;
+                b.k[tt][d] = kv[u][i] * km;
+            }
+        }
+        if (lane < kCV) b.v[tt][lane] = vv[u];
+    }
+}
+
+template <int DS, int MODE>
+__global__ void __launch_bounds__(2 * kCV *kNS) recurrence_kernel(rec_args p) {
+    extern __shared__ __align__(16) unsigned char rec_raw[];
+    rec_smem<DS> *buf = reinterpret_cast<rec_smem<DS> *>(rec_raw);
     const int h = blockIdx.x, col0 = blockIdx.y * kCV;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int s = tid % kNS, cl = tid / kNS, col = col0 + cl;
-    const bool live = col < p.Dv;
+    const bool producer = warp >= (kCV * kNS) / 32;
+    const int s = tid % kNS, cl = (tid / kNS) % kCV, col = col0 + cl;
+    const bool live = !producer && col < p.Dv;
     const int hk = MODE == 1 ? h / (p.H / p.G) : h; // the q / k head this head reads
     float S[DS];
     float *sp = p.state + ((int64_t)h * p.D) * p.Dv + col;
@@ -122,105 +195,74 @@ __global__ void __launch_bounds__(kCV *kNS) recurrence_kernel(rec_args p) {
     const float decay = MODE == 0 ? p.decay[h] : 0.f;
     const float a_rate = MODE == 1 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
     const float q_scale = 1.0f / sqrtf((float)p.D);
-    for (int64_t t0 = 0; t0 < p.T; t0 += kChunk) {
+    const int pw = warp - (kCV * kNS) / 32;
+    if (producer) rec_stage<DS, MODE>(p, buf[0], 0, (int)min((int64_t)kChunk, p.T), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
+    __syncthreads();
+    int cur = 0;
+    for (int64_t t0 = 0; t0 < p.T; t0 += kChunk, cur ^= 1) {
         const int n = (int)min((int64_t)kChunk, p.T - t0);
-        __syncthreads(); // the previous chunk has been consumed
-        // stage: a warp takes tokens warp, warp + 4, ...
-        for (int tt = warp; tt < n; tt += (kCV * kNS) / 32) {
-            const float *qr = p.q + (t0 + tt) * p.ld + (int64_t)hk * p.D, *kr = p.k + (t0 + tt) * p.ld + (int64_t)hk * p.D;
-            float qs = 0.f, ks = 0.f;
-            for (int d = lane; d < DP; d += 32) {
-                float qv = 0.f, kv = 0.f;
-                if (d < p.D) {
-                    qv = qr[d];
-                    kv = kr[d];
-                    if (MODE == 0) {
-                        qv = silu_f32(qv);
-                        kv = silu_f32(kv);
+        if (producer) {
+            if (t0 + kChunk < p.T)
+                rec_stage<DS, MODE>(p, buf[cur ^ 1], t0 + kChunk, (int)min((int64_t)kChunk, p.T - t0 - kChunk), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
+        } else {
+            const rec_smem<DS> &b = buf[cur];
+            for (int tt = 0; tt < n; tt++) {
+                const float4 *k4 = reinterpret_cast<const float4 *>(&b.k[tt][s * DS]);
+                const float4 *q4 = reinterpret_cast<const float4 *>(&b.q[tt][s * DS]);
+                float o0 = 0.f, o1 = 0.f;
+                if (MODE == 0) {
+                    const float vj = b.v[tt][cl];
+#pragma unroll
+                    for (int i = 0; i < DS / 4; i++) {
+                        const float4 kk = k4[i], qq = q4[i];
+                        S[4 * i + 0] = fmaf(kk.x, vj, decay * S[4 * i + 0]);
+                        S[4 * i + 1] = fmaf(kk.y, vj, decay * S[4 * i + 1]);
+                        S[4 * i + 2] = fmaf(kk.z, vj, decay * S[4 * i + 2]);
+                        S[4 * i + 3] = fmaf(kk.w, vj, decay * S[4 * i + 3]);
+                        o0 = fmaf(S[4 * i + 0], qq.x, o0);
+                        o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                        o0 = fmaf(S[4 * i + 2], qq.z, o0);
+                        o1 = fmaf(S[4 * i + 3], qq.w, o1);
+                    }
+                } else {
+                    const float g = b.g[tt];
+                    float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+                    for (int i = 0; i < DS / 4; i++) {
+                        const float4 kk = k4[i];
+                        S[4 * i + 0] *= g;
+                        S[4 * i + 1] *= g;
+                        S[4 * i + 2] *= g;
+                        S[4 * i + 3] *= g;
+                        r0 = fmaf(S[4 * i + 0], kk.x, r0);
+                        r1 = fmaf(S[4 * i + 1], kk.y, r1);
+                        r0 = fmaf(S[4 * i + 2], kk.z, r0);
+                        r1 = fmaf(S[4 * i + 3], kk.w, r1);
+                    }
+                    float r = r0 + r1;
+                    r += __shfl_xor_sync(0xffffffffu, r, 1);
+                    r += __shfl_xor_sync(0xffffffffu, r, 2);
+                    const float u = b.beta[tt] * (b.v[tt][cl] - r);
+#pragma unroll
+                    for (int i = 0; i < DS / 4; i++) {
+                        const float4 kk = k4[i], qq = q4[i];
+                        S[4 * i + 0] = fmaf(kk.x, u, S[4 * i + 0]);
+                        S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
+                        S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
+                        S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
+                        o0 = fmaf(S[4 * i + 0], qq.x, o0);
+                        o1 = fmaf(S[4 * i + 1], qq.y, o1);
+                        o0 = fmaf(S[4 * i + 2], qq.z, o0);
+                        o1 = fmaf(S[4 * i + 3], qq.w, o1);
                     }
                 }
-                sq[tt][d] = qv;
-                sk[tt][d] = kv;
-                qs = fmaf(qv, qv, qs);
-                ks = fmaf(kv, kv, ks);
-            }
-            if (MODE == 1) {
-                qs = warp_sum_f32(qs);
-                ks = warp_sum_f32(ks);
-                const float qm = q_scale / sqrtf(qs + 1e-6f), km = 1.0f / sqrtf(ks + 1e-6f);
-                __syncwarp();
-                for (int d = lane; d < DP; d += 32) {
-                    sq[tt][d] *= qm;
-                    sk[tt][d] *= km;
-                }
-                if (lane == 0) {
-                    sbeta[tt] = sigmoid_f32(p.b[(t0 + tt) * p.ld_ba + h]);
-                    sg[tt] = expf(-a_rate * softplus_f32(p.a[(t0 + tt) * p.ld_ba + h] + dtb));
-                }
-            }
-            const float *vr = p.v + (t0 + tt) * p.ld + (int64_t)h * p.Dv + col0;
-            if (lane < kCV) {
-                float vv = col0 + lane < p.Dv ? vr[lane] : 0.f;
-                if (MODE == 0) vv = silu_f32(vv);
-                sv[tt][lane] = vv;
+                float o = o0 + o1;
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+                if (s == 0 && live) p.o[(t0 + tt) * p.ldo + (int64_t)h * p.Dv + col] = o;
             }
         }
-        __syncthreads();
-        for (int tt = 0; tt < n; tt++) {
-            const float4 *k4 = reinterpret_cast<const float4 *>(&sk[tt][s * DS]);
-            const float4 *q4 = reinterpret_cast<const float4 *>(&sq[tt][s * DS]);
-            float o0 = 0.f, o1 = 0.f;
-            if (MODE == 0) {
-                const float vj = sv[tt][cl];
-#pragma unroll
-                for (int i = 0; i < DS / 4; i++) {
-                    const float4 kk = k4[i], qq = q4[i];
-                    S[4 * i + 0] = fmaf(kk.x, vj, decay * S[4 * i + 0]);
-                    S[4 * i + 1] = fmaf(kk.y, vj, decay * S[4 * i + 1]);
-                    S[4 * i + 2] = fmaf(kk.z, vj, decay * S[4 * i + 2]);
-                    S[4 * i + 3] = fmaf(kk.w, vj, decay * S[4 * i + 3]);
-                    o0 = fmaf(S[4 * i + 0], qq.x, o0);
-                    o1 = fmaf(S[4 * i + 1], qq.y, o1);
-                    o0 = fmaf(S[4 * i + 2], qq.z, o0);
-                    o1 = fmaf(S[4 * i + 3], qq.w, o1);
-                }
-            } else {
-                const float g = sg[tt];
-                float r0 = 0.f, r1 = 0.f;
-#pragma unroll
-                for (int i = 0; i < DS / 4; i++) {
-                    const float4 kk = k4[i];
-                    S[4 * i + 0] *= g;
-                    S[4 * i + 1] *= g;
-                    S[4 * i + 2] *= g;
-                    S[4 * i + 3] *= g;
-                    r0 = fmaf(S[4 * i + 0], kk.x, r0);
-                    r1 = fmaf(S[4 * i + 1], kk.y, r1);
-                    r0 = fmaf(S[4 * i + 2], kk.z, r0);
-                    r1 = fmaf(S[4 * i + 3], kk.w, r1);
-                }
-                float r = r0 + r1;
-                r += __shfl_xor_sync(0xffffffffu, r, 1);
-                r += __shfl_xor_sync(0xffffffffu, r, 2);
-                const float u = sbeta[tt] * (sv[tt][cl] - r);
-#pragma unroll
-                for (int i = 0; i < DS / 4; i++) {
-                    const float4 kk = k4[i], qq = q4[i];
-                    S[4 * i + 0] = fmaf(kk.x, u, S[4 * i + 0]);
-                    S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
-                    S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
-                    S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
-                    o0 = fmaf(S[4 * i + 0], qq.x, o0);
-                    o1 = fmaf(S[4 * i + 1], qq.y, o1);
-                    o0 = fmaf(S[4 * i + 2], qq.z, o0);
-                    o1 = fmaf(S[4 * i + 3], qq.w, o1);
-                }
-            }
-            float o = o0 + o1;
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (s == 0 && live) p.o[(t0 + tt) * p.ldo + (int64_t)h * p.Dv + col] = o;
-        }
+        __syncthreads(); // the chunk is consumed and the next one is staged
     }
 #pragma unroll
     for (int i = 0; i < DS; i++) {
@@ -229,17 +271,24 @@ __global__ void __launch_bounds__(kCV *kNS) recurrence_kernel(rec_args p) {
     }
 }
 
-template <int MODE>
-int recurrence_launch(const rec_args &p) {
+template <int DS, int MODE>
+int recurrence_launch_ds(const rec_args &p) {
     const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + kCV - 1) / kCV));
-    const int ds = (p.D + kNS - 1) / kNS;
-    cudaStream_t st = ggb_cuda_stream();
-    if (ds <= 8) recurrence_kernel<8, MODE><<<grid, kCV * kNS, 0, st>>>(p);
-    else if (ds <= 16) recurrence_kernel<16, MODE><<<grid, kCV * kNS, 0, st>>>(p);
-    else if (ds <= 32) recurrence_kernel<32, MODE><<<grid, kCV * kNS, 0, st>>>(p);
-    else recurrence_kernel<64, MODE><<<grid, kCV * kNS, 0, st>>>(p);
+    const size_t smem = 2 * sizeof(rec_smem<DS>);
+    auto k = recurrence_kernel<DS, MODE>;
+    if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k<<<grid, 2 * kCV * kNS, smem, ggb_cuda_stream()>>>(p);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
+}
+
+template <int MODE>
+int recurrence_launch(const rec_args &p) {
+    const int ds = (p.D + kNS - 1) / kNS;
+    if (ds <= 8) return recurrence_launch_ds<8, MODE>(p);
+    if (ds <= 16) return recurrence_launch_ds<16, MODE>(p);
+    if (ds <= 32) return recurrence_launch_ds<32, MODE>(p);
+    return recurrence_launch_ds<64, MODE>(p);
 }
 
 } // namespace

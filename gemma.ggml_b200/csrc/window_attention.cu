@@ -6,10 +6,13 @@
 // on the device (a captured one-token step replays anywhere).  Scores, soft-max and the weighted sum are fp32.
 //
 // qkv_store: one CTA per token: root mean square over the whole q and the whole k projection, weights, rotation, store.
-// window_attn: a warp owns (token, head[, split of the keys]); lane = key for the scores (its row read with 16-byte
-// loads), lane = pair of value coordinates for the weighted sum (rows read coalesced), running maximum and sum in
-// registers.  Portions: 8 consecutive tokens of one head per CTA (their windows overlap: the rows meet in L1);
-// a step of few tokens: 8 warps split one (token, head)'s keys and merge through shared memory.
+// window_attn, both forms: lane = key for the scores, lane = pair of value coordinates for the weighted sum, running
+// maximum and sum in registers.
+//   portions (window_attn_tile_kernel): a CTA owns 32 consecutive tokens of one head, 4 per warp.  Their windows
+//   overlap almost wholly, so every tile of 32 cache rows is staged once in shared memory as fp32 (row pitch odd in words:
+//   lane = row reads are conflict-free) and serves all 32 queries; a K word read feeds 4 multiply-adds.
+//   steps of few tokens (window_attn_kernel): 8 warps split one (token, head)'s keys, rows straight from the cache
+//   (several loads in flight), parts merged through shared memory.
 //
 // Compiled with -fmad=false: multiply-adds are spelled fmaf().
 #include "common.cuh"
@@ -138,6 +141,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
                 float a0 = 0.f, a1 = 0.f;
                 if (vec) {
                     constexpr int VN = RowVec<E>::n;
+#pragma unroll 4
                     for (int d = 0; d < D; d += VN) {
                         RowVec<E> kv;
                         kv.raw = *reinterpret_cast<const uint4 *>(kr + d);
@@ -160,16 +164,33 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
             for (int r = 0; r < kMaxDvRegs; r++) acc[r] *= corr;
             m = m_new;
             const int n_keys = (int)min((int64_t)32, i - j0 + 1);
-            for (int jj = 0; jj < n_keys; jj++) {
-                const float pj = __shfl_sync(0xffffffffu, p, jj);
-                const int64_t jr = j0 + jj;
-                const E *vr = cache + ((int64_t)table[jr / B] * B + jr % B) * cache_ld + voff;
+            // rows in groups of 8: the loads of a group are independent and in flight together (a row past the last
+            // visible one repeats it with weight 0)
+            for (int jb = 0; jb < n_keys; jb += 8) {
+                const E *vrow[8];
+                float pj[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int jj = min(jb + u, n_keys - 1);
+                    pj[u] = jb + u < n_keys ? __shfl_sync(0xffffffffu, p, jj) : 0.f;
+                    const int64_t jr = j0 + jj;
+                    vrow[u] = cache + ((int64_t)table[jr / B] * B + jr % B) * cache_ld + voff;
+                }
 #pragma unroll
                 for (int r = 0; r < kMaxDvRegs / 2; r++) {
                     const int c = 2 * lane + 64 * r;
                     if (r < nreg && c < Dv) {
-                        acc[2 * r] = fmaf(pj, to_f32(vr[c]), acc[2 * r]);
-                        acc[2 * r + 1] = fmaf(pj, to_f32(vr[c + 1]), acc[2 * r + 1]);
+                        float v0[8], v1[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            v0[u] = to_f32(vrow[u][c]);
+                            v1[u] = to_f32(vrow[u][c + 1]);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            acc[2 * r] = fmaf(pj[u], v0[u], acc[2 * r]);
+                            acc[2 * r + 1] = fmaf(pj[u], v1[u], acc[2 * r + 1]);
+                        }
                     }
                 }
             }
@@ -221,6 +242,134 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
     }
 }
 
+// ---- portions: 32 tokens of one head per CTA, tiles of 32 cache rows staged in shared memory
+constexpr int kQT = 32, kQPW = kQT / kWarps; // queries per CTA and per warp
+
+template <typename E>
+__global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
+                                                                       const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
+                                                                       int64_t T, int H, int G, int D, int Dv, int64_t window,
+                                                                       const float *__restrict__ cs_v, E *__restrict__ out) {
+    extern __shared__ __align__(16) float wa_smem[];
+    const int Dp = (D + 3) & ~3, kp = D | 1, vp = Dv + 2; // pitches in words: q rows 16-byte aligned, K rows odd, V rows even (float2 reads)
+    float *sq = wa_smem;              // [kQT][Dp]
+    float *sk = sq + kQT * Dp;        // [32][kp]
+    float *sv = sk + 32 * kp;         // [32][vp]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y, g = h / (H / G);
+    const int64_t t0 = (int64_t)blockIdx.x * kQT;
+    const int nq = (int)min((int64_t)kQT, T - t0);
+    const int64_t i0 = (int64_t)*pos0 + t0;          // position of the CTA's first query
+    const int64_t i_last = i0 + nq - 1;
+    for (int e = threadIdx.x; e < kQT * Dp; e += blockDim.x) {
+        const int qi = e / Dp, d = e - qi * Dp;
+        sq[e] = (qi < nq && d < D) ? q[((t0 + qi) * H + h) * D + d] : 0.f;
+    }
+    const int64_t jlo = window > 0 ? max((int64_t)0, i0 - window + 1) : 0;
+    const int nreg = (Dv + 63) / 64;
+    float acc[kQPW][kMaxDvRegs], m[kQPW], l[kQPW];
+#pragma unroll
+    for (int a = 0; a < kQPW; a++) {
+        m[a] = -INFINITY;
+        l[a] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs; r++) acc[a][r] = 0.f;
+    }
+    const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
+    const int row_elems = D + Dv;
+    for (int64_t j0 = jlo; j0 <= i_last; j0 += 32) {
+        __syncthreads(); // the previous tile has been consumed (and sq is written, the first time)
+        const int n_rows = (int)min((int64_t)32, i_last - j0 + 1);
+        for (int e = threadIdx.x; e < 32 * row_elems; e += blockDim.x) {
+            const int rr = e / row_elems, c = e - rr * row_elems;
+            float val = 0.f;
+            if (rr < n_rows) {
+                const int64_t j = j0 + rr;
+                const E *row = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld;
+                val = to_f32(c < D ? row[koff + c] : row[voff + c - D]);
+            }
+            if (c < D) sk[rr * kp + c] = val;
+            else sv[rr * vp + c - D] = val;
+        }
+        __syncthreads();
+        // scores of the warp's queries against key j0 + lane
+        float s[kQPW];
+#pragma unroll
+        for (int a = 0; a < kQPW; a++) s[a] = 0.f;
+        const float *kr = sk + lane * kp;
+        for (int d = 0; d < D; d += 4) { // Dp words of every q row are there (zeros past D); K words past D are not read
+            float kv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) kv[u] = d + u < D ? kr[d + u] : 0.f;
+#pragma unroll
+            for (int a = 0; a < kQPW; a++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(sq + (warp * kQPW + a) * Dp + d);
+                s[a] = fmaf(kv[0], qv.x, s[a]);
+                s[a] = fmaf(kv[1], qv.y, s[a]);
+                s[a] = fmaf(kv[2], qv.z, s[a]);
+                s[a] = fmaf(kv[3], qv.w, s[a]);
+            }
+        }
+        float p[kQPW];
+        const int64_t j = j0 + lane;
+#pragma unroll
+        for (int a = 0; a < kQPW; a++) {
+            const int64_t i = i0 + warp * kQPW + a;
+            const bool live = warp * kQPW + a < nq;
+            const bool vis = live && j <= i && (window <= 0 || i - j < window);
+            const float sa = vis ? s[a] : -INFINITY;
+            const float m_new = fmaxf(m[a], warp_max_f32(sa));
+            // a query none of whose keys lie in this tile keeps m = -inf: nothing to rescale, nothing to add
+            const float corr = m_new == -INFINITY ? 1.f : expf(m[a] - m_new);
+            p[a] = vis ? expf(sa - m_new) : 0.f;
+            l[a] = l[a] * corr + warp_sum_f32(p[a]);
+#pragma unroll
+            for (int r = 0; r < kMaxDvRegs; r++) acc[a][r] *= corr;
+            m[a] = m_new;
+        }
+        for (int jj = 0; jj < n_rows; jj++) {
+            float pj[kQPW];
+#pragma unroll
+            for (int a = 0; a < kQPW; a++) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
+#pragma unroll
+            for (int r = 0; r < kMaxDvRegs / 2; r++) {
+                const int c = 2 * lane + 64 * r;
+                if (r < nreg && c < Dv) {
+                    const float2 vv = *reinterpret_cast<const float2 *>(sv + jj * vp + c);
+#pragma unroll
+                    for (int a = 0; a < kQPW; a++) {
+                        acc[a][2 * r] = fmaf(pj[a], vv.x, acc[a][2 * r]);
+                        acc[a][2 * r + 1] = fmaf(pj[a], vv.y, acc[a][2 * r + 1]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < kQPW; a++) {
+        const int qi = warp * kQPW + a;
+        if (qi >= nq) continue;
+        const int64_t t = t0 + qi, i = i0 + qi;
+        const float inv = 1.0f / l[a];
+        const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs / 2; r++) {
+            const int c = 2 * lane + 64 * r;
+            if (r < nreg && c < Dv) {
+                float u = acc[a][2 * r] * inv, w = acc[a][2 * r + 1] * inv;
+                if (cv) {
+                    const float cs = cv[c], sn = cv[c + 1];
+                    const float u2 = u * cs + w * sn, w2 = w * cs - u * sn;
+                    u = u2;
+                    w = w2;
+                }
+                out[(t * H + h) * Dv + c] = from_f32<E>(u);
+                out[(t * H + h) * Dv + c + 1] = from_f32<E>(w);
+            }
+        }
+    }
+}
+
 } // namespace
 
 extern "C" {
@@ -260,20 +409,30 @@ int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t 
     const int Dp = (D + 3) & ~3;
     const int es = dt == GGB_TYPE_BF16 ? 2 : 4, vn = 16 / es;
     const int vec = D % vn == 0 && ((uintptr_t)cache % 16 == 0); // rows are 8 numbers apart at least: 16-byte aligned in both types
-    const bool split = T < 4 * kWarps;
-    const size_t smem = (size_t)kWarps * Dp * 4 + (split ? (size_t)kWarps * (2 + 32 * kMaxDvRegs) * 4 : 0);
-    GGB_CHECK_ARG(smem <= 48 * 1024, "window_attn: key size %d does not fit shared memory", D);
     cudaStream_t st = ggb_cuda_stream();
-#define WA_LAUNCH(ET)                                                                                                                       \
-    if (split)                                                                                                                              \
-        window_attn_kernel<ET, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table,      \
-                                                                                                block_size, pos0, T, H, G, D, Dv, window,   \
-                                                                                                cos_sin_v, (ET *)out, vec);                 \
-    else                                                                                                                                    \
-        window_attn_kernel<ET, false><<<dim3((unsigned)((T + kWarps - 1) / kWarps), (unsigned)H), 32 * kWarps, smem, st>>>(                  \
-            q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (ET *)out, vec);
-    if (dt == GGB_TYPE_BF16) { WA_LAUNCH(__nv_bfloat16) } else { WA_LAUNCH(float) }
-#undef WA_LAUNCH
+    if (T >= kQT) { // a portion: tiles of cache rows staged once for 32 queries
+        const size_t smem = ((size_t)kQT * Dp + 32 * (size_t)(D | 1) + 32 * (size_t)(Dv + 2)) * 4;
+        GGB_CHECK_ARG(smem <= 200 * 1024, "window_attn: head sizes %d / %d do not fit shared memory", D, Dv);
+        const dim3 grid((unsigned)((T + kQT - 1) / kQT), (unsigned)H);
+#define WT_LAUNCH(ET)                                                                                                        \
+    {                                                                                                                        \
+        auto kfn = window_attn_tile_kernel<ET>;                                                                              \
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+        kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, \
+                                             cos_sin_v, (ET *)out);                                                          \
+    }
+        if (dt == GGB_TYPE_BF16) WT_LAUNCH(__nv_bfloat16) else WT_LAUNCH(float)
+#undef WT_LAUNCH
+    } else {
+        const size_t smem = (size_t)kWarps * Dp * 4 + (size_t)kWarps * (2 + 32 * kMaxDvRegs) * 4;
+        GGB_CHECK_ARG(smem <= 48 * 1024, "window_attn: key size %d does not fit shared memory", D);
+        if (dt == GGB_TYPE_BF16)
+            window_attn_kernel<__nv_bfloat16, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(
+                q, (const __nv_bfloat16 *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (__nv_bfloat16 *)out, vec);
+        else
+            window_attn_kernel<float, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(
+                q, (const float *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (float *)out, vec);
+    }
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

@@ -114,7 +114,7 @@ def test_glu_bias_softcap_and_normed_gate(gpu, dt):
     zd = dev(gpu, z)
     gpu.check(gpu.cuda_lib().ggb_op_softcap(zd.ptr, 50, 11.0), "softcap")
     assert F.rel_err(zd.download(np.float32, 50), 11.0 * np.tanh(z.astype(np.float64) / 11.0)) < 1e-6
-    for n_groups, gs, period, act in ((1, 21, 21, 0), (3, 7, 7, 1), (2, 40, 80, 1)):
+    for n_groups, gs, period, act in ((1, 21, 21, 0), (3, 7, 7, 1), (2, 40, 80, 1), (1, 777, 777, 0), (2, 512, 512, 1)):
         ld_o, ld_g = n_groups * gs + 3, n_groups * gs + 5
         o, g, w = f32(r.standard_normal((T, ld_o))), f32(r.standard_normal((T, ld_g))), f32(1 + 0.2 * r.standard_normal(period))
         y = zeros(gpu, T * n_groups * gs * es)
