@@ -150,7 +150,8 @@ _CUDA_SIG = {
     "ggb_op_gated_delta": (i32, [vp, vp, vp, i64, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, i64]),
     "ggb_window_cache_ld": (i64, [i32, i32, i32]),
     "ggb_op_window_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, f32, i32, vp, vp, f32, vp, vp, i32, vp, vp]),
-    "ggb_op_window_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp]),
+    "ggb_op_window_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp, vp]),
+    "ggb_window_attn_scratch_bytes": (sz, [i32]),
     "ggb_op_moe_route": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp, vp]),
     "ggb_moe_max_tiles": (i32, [i64, i32]), "ggb_moe_group_ints": (sz, [i64, i32]),
     "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),

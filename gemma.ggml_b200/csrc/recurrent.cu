@@ -106,10 +106,14 @@ struct rec_args {
 //
 // 256 threads: threads 0..127 run the recurrence on the chunk in one buffer while warps 4..7 stage the next chunk into
 // the other (global loads of a warp's four tokens in flight together), one barrier per chunk.
+// A lane's slice of a q / k row starts DS + 4 words after its neighbour's: the four 16-byte reads of a warp fall into
+// four different groups of banks (DS alone is a multiple of 8 words: all four would meet in one).
 template <int DS>
 struct rec_smem {
-    static constexpr int DP = DS * kNS; // padded D
-    float q[kChunk][DP], k[kChunk][DP];
+    static constexpr int DP = DS * kNS;        // padded D
+    static constexpr int DW = (DS + 4) * kNS;  // words of a staged row
+    __device__ static __forceinline__ int at(int d) { return (d / DS) * (DS + 4) + d % DS; }
+    float q[kChunk][DW], k[kChunk][DW];
     float v[kChunk][kCV], g[kChunk], beta[kChunk];
 };
 
@@ -167,8 +171,8 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, in
         for (int i = 0; i < PL; i++) {
             const int d = lane + 32 * i;
             if (d < DP) {
-                b.q[tt][d] = qv[u][i] * qm;
-                b.k[tt][d] = kv[u][i] * km;
+                b.q[tt][rec_smem<DS>::at(d)] = qv[u][i] * qm;
+                b.k[tt][rec_smem<DS>::at(d)] = kv[u][i] * km;
             }
         }
         if (lane < kCV) b.v[tt][lane] = vv[u];
@@ -207,8 +211,8 @@ __global__ void __launch_bounds__(2 * kCV *kNS) recurrence_kernel(rec_args p) {
         } else {
             const rec_smem<DS> &b = buf[cur];
             for (int tt = 0; tt < n; tt++) {
-                const float4 *k4 = reinterpret_cast<const float4 *>(&b.k[tt][s * DS]);
-                const float4 *q4 = reinterpret_cast<const float4 *>(&b.q[tt][s * DS]);
+                const float4 *k4 = reinterpret_cast<const float4 *>(&b.k[tt][s * (DS + 4)]);
+                const float4 *q4 = reinterpret_cast<const float4 *>(&b.q[tt][s * (DS + 4)]);
                 float o0 = 0.f, o1 = 0.f;
                 if (MODE == 0) {
                     const float vj = b.v[tt][cl];

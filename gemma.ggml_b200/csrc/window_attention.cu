@@ -15,6 +15,8 @@
 //   (several loads in flight), parts merged through shared memory.
 //
 // Compiled with -fmad=false: multiply-adds are spelled fmaf().
+#include <algorithm>
+
 #include "common.cuh"
 #include "dense.cuh"
 
@@ -22,6 +24,7 @@ namespace {
 
 constexpr int kMaxDvRegs = 8; // value coordinates per lane: Dv <= 32 * kMaxDvRegs
 constexpr int kWarps = 8;
+constexpr int kMaxSplit = 16; // CTAs that share one (token, head) of a short step
 
 template <typename E>
 __global__ void __launch_bounds__(256) window_qkv_store_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
@@ -106,18 +109,45 @@ template <typename E> struct RowVec { // 16 bytes of a cache row
     __device__ __forceinline__ float at(int i) const { return to_f32(reinterpret_cast<const E *>(&raw)[i]); }
 };
 
-// SPLIT false: warp w of the CTA owns token blockIdx.x * 8 + w, all of its keys.  SPLIT true: the CTA owns token blockIdx.x
-// and warp w takes the key tiles w, w + 8, ...
-template <typename E, bool SPLIT>
+// what a head's weighted sum becomes: divided by the soft-max sum, turned back by the reader's position, stored
+template <typename E>
+__device__ __forceinline__ void window_finish(const float *acc, float l, int64_t i, int lane, int Dv, const float *__restrict__ cs_v, E *orow) {
+    const int nreg = (Dv + 63) / 64;
+    const float inv = 1.0f / l;
+    const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
+#pragma unroll
+    for (int r = 0; r < kMaxDvRegs / 2; r++) {
+        const int c = 2 * lane + 64 * r;
+        if (r < nreg && c < Dv) {
+            float u = acc[2 * r] * inv, w = acc[2 * r + 1] * inv;
+            if (cv) { // turned back: by -i
+                const float cs = cv[c], sn = cv[c + 1];
+                const float u2 = u * cs + w * sn, w2 = w * cs - u * sn;
+                u = u2;
+                w = w2;
+            }
+            orow[c] = from_f32<E>(u);
+            orow[c + 1] = from_f32<E>(w);
+        }
+    }
+}
+
+constexpr int kPartW = 2 + 32 * kMaxDvRegs; // one part: running maximum, sum, weighted sum as the lanes hold it
+
+// The CTA (token blockIdx.x, head blockIdx.y, split blockIdx.z of gridDim.z) takes the key tiles whose number is
+// split * 8 + warp modulo 8 * splits, one warp a tile.  One split: the result goes to `out`; several: the CTA's merged
+// part goes to `part` and window_merge_kernel finishes.
+template <typename E>
 __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
                                                                   int64_t T, int H, int G, int D, int Dv, int64_t window,
-                                                                  const float *__restrict__ cs_v, E *__restrict__ out, int vec) {
-    extern __shared__ __align__(16) float wa_smem[]; // q: [kWarps][Dp]; merge: [kWarps][2 + 64 * kMaxDvRegs / 2 ...]
+                                                                  const float *__restrict__ cs_v, E *__restrict__ out, int vec,
+                                                                  float *__restrict__ part_out) {
+    extern __shared__ __align__(16) float wa_smem[]; // q: [kWarps][Dp]; merge: [kWarps][kPartW]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y, g = h / (H / G);
     const int Dp = (D + 3) & ~3;
-    const int64_t t = SPLIT ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp;
+    const int64_t t = blockIdx.x;
     const bool active = t < T;
     float *sq = wa_smem + warp * Dp;
     if (active)
@@ -132,8 +162,8 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
     float m = -INFINITY, l = 0.f;
     const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
     if (active) {
-        const int64_t step = SPLIT ? 32 * kWarps : 32;
-        for (int64_t j0 = jlo + (SPLIT ? 32 * warp : 0); j0 <= i; j0 += step) {
+        const int64_t step = 32 * kWarps * (int64_t)gridDim.z;
+        for (int64_t j0 = jlo + 32 * ((int64_t)blockIdx.z * kWarps + warp); j0 <= i; j0 += step) {
             const int64_t j = j0 + lane;
             float s = -INFINITY;
             if (j <= i) {
@@ -196,10 +226,10 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
             }
         }
     }
-    if (SPLIT) { // merge the warps' parts: [m, l, acc...] per warp
+    { // merge the warps' parts: [m, l, acc...] per warp
         __syncthreads();
         float *part = wa_smem + kWarps * Dp;
-        const int pw = 2 + 32 * kMaxDvRegs;
+        const int pw = kPartW;
         if (lane == 0) {
             part[warp * pw] = m;
             part[warp * pw + 1] = l;
@@ -221,25 +251,42 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
 #pragma unroll
             for (int r = 0; r < kMaxDvRegs; r++) acc[r] = fmaf(part[w * pw + 2 + r * 32 + lane], f, acc[r]);
         }
+        m = M;
     }
-    if (!active) return;
-    const float inv = 1.0f / l;
-    const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
-#pragma unroll
-    for (int r = 0; r < kMaxDvRegs / 2; r++) {
-        const int c = 2 * lane + 64 * r;
-        if (r < nreg && c < Dv) {
-            float u = acc[2 * r] * inv, w = acc[2 * r + 1] * inv;
-            if (cv) { // turned back: by -i
-                const float cs = cv[c], sn = cv[c + 1];
-                const float u2 = u * cs + w * sn, w2 = w * cs - u * sn;
-                u = u2;
-                w = w2;
-            }
-            out[(t * H + h) * Dv + c] = from_f32<E>(u);
-            out[(t * H + h) * Dv + c + 1] = from_f32<E>(w);
+    if (gridDim.z > 1) { // M = -inf, l = 0 when the split had no tile
+        float *po = part_out + ((t * H + h) * gridDim.z + blockIdx.z) * kPartW;
+        if (lane == 0) {
+            po[0] = m;
+            po[1] = l;
         }
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs; r++) po[2 + r * 32 + lane] = acc[r];
+        return;
     }
+    window_finish(acc, l, i, lane, Dv, cs_v, out + (t * H + h) * Dv);
+}
+
+// one warp per (token, head): the splits' parts merged, then as above
+template <typename E>
+__global__ void __launch_bounds__(32) window_merge_kernel(const float *__restrict__ part, int n_split, const int32_t *__restrict__ pos0, int H, int Dv,
+                                                         const float *__restrict__ cs_v, E *__restrict__ out) {
+    const int64_t t = blockIdx.x;
+    const int h = blockIdx.y, lane = threadIdx.x;
+    const float *pp = part + ((t * H + h) * n_split) * kPartW;
+    float M = -INFINITY;
+    for (int s = 0; s < n_split; s++) M = fmaxf(M, pp[s * kPartW]);
+    float l = 0.f, acc[kMaxDvRegs];
+#pragma unroll
+    for (int r = 0; r < kMaxDvRegs; r++) acc[r] = 0.f;
+    for (int s = 0; s < n_split; s++) {
+        const float ms = pp[s * kPartW];
+        if (ms == -INFINITY) continue;
+        const float f = expf(ms - M);
+        l = fmaf(pp[s * kPartW + 1], f, l);
+#pragma unroll
+        for (int r = 0; r < kMaxDvRegs; r++) acc[r] = fmaf(pp[s * kPartW + 2 + r * 32 + lane], f, acc[r]);
+    }
+    window_finish(acc, l, (int64_t)*pos0 + t, lane, Dv, cs_v, out + (t * H + h) * Dv);
 }
 
 // ---- portions: 32 tokens of one head per CTA, tiles of 32 cache rows staged in shared memory
@@ -249,7 +296,7 @@ template <typename E>
 __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                        const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
                                                                        int64_t T, int H, int G, int D, int Dv, int64_t window,
-                                                                       const float *__restrict__ cs_v, E *__restrict__ out) {
+                                                                       const float *__restrict__ cs_v, E *__restrict__ out, int vec) {
     extern __shared__ __align__(16) float wa_smem[];
     const int Dp = (D + 3) & ~3, kp = D | 1, vp = Dv + 2; // pitches in words: q rows 16-byte aligned, K rows odd, V rows even (float2 reads)
     float *sq = wa_smem;              // [kQT][Dp]
@@ -278,18 +325,31 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
     const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
     const int row_elems = D + Dv;
     for (int64_t j0 = jlo; j0 <= i_last; j0 += 32) {
+
         __syncthreads(); // the previous tile has been consumed (and sq is written, the first time)
         const int n_rows = (int)min((int64_t)32, i_last - j0 + 1);
-        for (int e = threadIdx.x; e < 32 * row_elems; e += blockDim.x) {
-            const int rr = e / row_elems, c = e - rr * row_elems;
-            float val = 0.f;
-            if (rr < n_rows) {
-                const int64_t j = j0 + rr;
-                const E *row = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld;
-                val = to_f32(c < D ? row[koff + c] : row[voff + c - D]);
+        // a warp stages rows warp, warp + 8, ...: 16-byte pieces of the K part and of the V part, converted to fp32
+        for (int rr = warp; rr < 32; rr += kWarps) {
+            const int64_t j = j0 + min(rr, n_rows - 1); // a row past the last one repeats it (masked below, weight 0)
+            const E *row = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld;
+            if (vec) {
+                constexpr int VN = RowVec<E>::n;
+                const int nk = D / VN, nv = Dv / VN;
+                for (int vi = lane; vi < nk + nv; vi += 32) {
+                    const bool is_k = vi < nk;
+                    const int c = (is_k ? vi : vi - nk) * VN;
+                    RowVec<E> x;
+                    x.raw = *reinterpret_cast<const uint4 *>(row + (is_k ? koff : voff) + c);
+                    float *dst = is_k ? sk + rr * kp + c : sv + rr * vp + c;
+#pragma unroll
+                    for (int u = 0; u < VN; u++) dst[u] = x.at(u);
+                }
+            } else {
+                for (int c = lane; c < row_elems; c += 32) {
+                    if (c < D) sk[rr * kp + c] = to_f32(row[koff + c]);
+                    else sv[rr * vp + c - D] = to_f32(row[voff + c - D]);
+                }
             }
-            if (c < D) sk[rr * kp + c] = val;
-            else sv[rr * vp + c - D] = val;
         }
         __syncthreads();
         // scores of the warp's queries against key j0 + lane
@@ -297,19 +357,22 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
 #pragma unroll
         for (int a = 0; a < kQPW; a++) s[a] = 0.f;
         const float *kr = sk + lane * kp;
-        for (int d = 0; d < D; d += 4) { // Dp words of every q row are there (zeros past D); K words past D are not read
-            float kv[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) kv[u] = d + u < D ? kr[d + u] : 0.f;
+        const int D4 = D & ~3;
+#pragma unroll 2
+        for (int d = 0; d < D4; d += 4) {
+            const float k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
 #pragma unroll
             for (int a = 0; a < kQPW; a++) {
                 const float4 qv = *reinterpret_cast<const float4 *>(sq + (warp * kQPW + a) * Dp + d);
-                s[a] = fmaf(kv[0], qv.x, s[a]);
-                s[a] = fmaf(kv[1], qv.y, s[a]);
-                s[a] = fmaf(kv[2], qv.z, s[a]);
-                s[a] = fmaf(kv[3], qv.w, s[a]);
+                s[a] = fmaf(k0, qv.x, s[a]);
+                s[a] = fmaf(k1, qv.y, s[a]);
+                s[a] = fmaf(k2, qv.z, s[a]);
+                s[a] = fmaf(k3, qv.w, s[a]);
             }
         }
+        for (int d = D4; d < D; d++)
+#pragma unroll
+            for (int a = 0; a < kQPW; a++) s[a] = fmaf(kr[d], sq[(warp * kQPW + a) * Dp + d], s[a]);
         float p[kQPW];
         const int64_t j = j0 + lane;
 #pragma unroll
@@ -349,24 +412,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
     for (int a = 0; a < kQPW; a++) {
         const int qi = warp * kQPW + a;
         if (qi >= nq) continue;
-        const int64_t t = t0 + qi, i = i0 + qi;
-        const float inv = 1.0f / l[a];
-        const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
-#pragma unroll
-        for (int r = 0; r < kMaxDvRegs / 2; r++) {
-            const int c = 2 * lane + 64 * r;
-            if (r < nreg && c < Dv) {
-                float u = acc[a][2 * r] * inv, w = acc[a][2 * r + 1] * inv;
-                if (cv) {
-                    const float cs = cv[c], sn = cv[c + 1];
-                    const float u2 = u * cs + w * sn, w2 = w * cs - u * sn;
-                    u = u2;
-                    w = w2;
-                }
-                out[(t * H + h) * Dv + c] = from_f32<E>(u);
-                out[(t * H + h) * Dv + c + 1] = from_f32<E>(w);
-            }
-        }
+        window_finish(acc[a], l[a], i0 + qi, lane, Dv, cs_v, out + ((t0 + qi) * H + h) * Dv);
     }
 }
 
@@ -398,8 +444,10 @@ int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float 
     return GGB_OK;
 }
 
+size_t ggb_window_attn_scratch_bytes(int H) { return (size_t)(kQT - 1) * (size_t)H * kMaxSplit * kPartW * 4; }
+
 int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
-                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out) {
+                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out, float *scratch) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "window_attn: dtype %d is neither bf16 nor f32", dt);
     GGB_CHECK_ARG(q && cache && block_table && pos0 && out && T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && D > 0 && Dv > 0 &&
@@ -419,19 +467,28 @@ int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t 
         auto kfn = window_attn_tile_kernel<ET>;                                                                              \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
         kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, \
-                                             cos_sin_v, (ET *)out);                                                          \
+                                             cos_sin_v, (ET *)out, vec && Dv % vn == 0);                                     \
     }
         if (dt == GGB_TYPE_BF16) WT_LAUNCH(__nv_bfloat16) else WT_LAUNCH(float)
 #undef WT_LAUNCH
     } else {
-        const size_t smem = (size_t)kWarps * Dp * 4 + (size_t)kWarps * (2 + 32 * kMaxDvRegs) * 4;
+        const size_t smem = (size_t)kWarps * Dp * 4 + (size_t)kWarps * kPartW * 4;
         GGB_CHECK_ARG(smem <= 48 * 1024, "window_attn: key size %d does not fit shared memory", D);
-        if (dt == GGB_TYPE_BF16)
-            window_attn_kernel<__nv_bfloat16, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(
-                q, (const __nv_bfloat16 *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (__nv_bfloat16 *)out, vec);
-        else
-            window_attn_kernel<float, true><<<dim3((unsigned)T, (unsigned)H), 32 * kWarps, smem, st>>>(
-                q, (const float *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, cos_sin_v, (float *)out, vec);
+        // a warp a tile: as many splits as the longest visible range has groups of 8 tiles (the range is bounded by the
+        // window; without one, by what the scratch was sized for)
+        int n_split = 1;
+        if (scratch && window > 0) n_split = (int)std::min<int64_t>(kMaxSplit, ((window + 62) / 32 + kWarps - 1) / kWarps);
+        else if (scratch) n_split = kMaxSplit / 2;
+        const dim3 grid((unsigned)T, (unsigned)H, (unsigned)n_split);
+#define WS_LAUNCH(ET)                                                                                                                        \
+    window_attn_kernel<ET><<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window,  \
+                                                            cos_sin_v, (ET *)out, vec, scratch);                                             \
+    if (n_split > 1) {                                                                                                                       \
+        GGB_LAUNCH_CHECK();                                                                                                                  \
+        window_merge_kernel<ET><<<dim3((unsigned)T, (unsigned)H), 32, 0, st>>>(scratch, n_split, pos0, H, Dv, cos_sin_v, (ET *)out);          \
+    }
+        if (dt == GGB_TYPE_BF16) { WS_LAUNCH(__nv_bfloat16) } else { WS_LAUNCH(float) }
+#undef WS_LAUNCH
     }
     GGB_LAUNCH_CHECK();
     return GGB_OK;

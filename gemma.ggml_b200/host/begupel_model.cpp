@@ -325,6 +325,7 @@ int begupel_model::alloc_scratch() {
     const bg_config &c = cfg_;
     const int64_t T = max_T_, W = c.width;
     int64_t npr = 0, ncv = 0, nq = 0, nro = 0, nao = 0, ff = 0;
+    int hmax = 1;
     for (size_t li = 0; li < c.layers.size(); li++) {
         const bg_layer_cfg &l = c.layers[li];
         npr = std::max(npr, lw_[li].n_proj);
@@ -334,6 +335,7 @@ int begupel_model::alloc_scratch() {
             ncv = std::max(ncv, 2 * (int64_t)l.right.kv_heads * l.right.dim + (int64_t)l.right.heads * l.right.vdim);
             nq = std::max(nq, (int64_t)l.left.heads * l.left.dim);
             nao = std::max(nao, (int64_t)l.left.heads * l.left.vdim);
+            hmax = std::max(hmax, l.left.heads);
             nro = std::max(nro, (int64_t)l.right.heads * l.right.vdim);
         }
         ff = std::max(ff, (int64_t)l.ff);
@@ -355,6 +357,7 @@ int begupel_model::alloc_scratch() {
     BG_ALLOC(cv_, T * ncv * 4);
     BG_ALLOC(qr_, T * nq * 4);
     BG_ALLOC(ao_, T * nao * es);
+    BG_ALLOC(wa_, ggb_window_attn_scratch_bytes(hmax));
     BG_ALLOC(ro_, T * nro * 4);
     BG_ALLOC(gd_, T * nro * es);
     BG_ALLOC(ya_, T * W * 4);
@@ -428,7 +431,7 @@ int begupel_model::emit(int T, const int32_t *table, float *state, int n_want) {
             const int64_t HV = (int64_t)A.heads * A.vdim;
             BG_OP("op_attn_prep", ggb_op_window_qkv_store(dt_, pr_ + w.o_q, pr_ + w.o_k, pr_ + w.o_v, N, t, A.heads, A.kv_heads, A.dim, A.vdim, w.qn,
                                                           w.kn, c.eps, A.rot.dims, w.cs_k, w.cs_v, A.scale, pos0_, table, B, cache, qr_));
-            BG_OP("op_attn", ggb_op_window_attn(dt_, qr_, cache, table, B, pos0_, t, A.heads, A.kv_heads, A.dim, A.vdim, A.window, w.cs_v, ao_));
+            BG_OP("op_attn", ggb_op_window_attn(dt_, qr_, cache, table, B, pos0_, t, A.heads, A.kv_heads, A.dim, A.vdim, A.window, w.cs_v, ao_, wa_));
             BG_OP("op_linear", ggb_op_linear(dt_, w.o, W, HV, ao_, HV, t, ya_, W));
             const int64_t GD = (int64_t)R.kv_heads * R.dim, RV = (int64_t)R.heads * R.vdim, C = 2 * GD + RV;
             BG_OP("op_conv", ggb_op_causal_conv(dt_, pr_ + w.o_rq, N, t, C, w.rconv, R.conv, 0, 1, R.conv > 1 ? state + w.s_rconv : nullptr, cv_, C, nullptr));

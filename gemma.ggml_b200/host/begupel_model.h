@@ -125,7 +125,7 @@ class begupel_model : public lm_model {
     std::map<std::string, float *> rot_tables_;
     int32_t *ids_ = nullptr, *pos0_ = nullptr, *want_ = nullptr, *iota_ = nullptr;
     float *x_ = nullptr, *pr_ = nullptr, *cv_ = nullptr, *qr_ = nullptr, *ro_ = nullptr, *ya_ = nullptr, *yb_ = nullptr, *gu_ = nullptr,
-          *xw_ = nullptr, *logits_ = nullptr, *cap_ = nullptr;
+          *xw_ = nullptr, *logits_ = nullptr, *cap_ = nullptr, *wa_ = nullptr;
     void *h_ = nullptr, *ao_ = nullptr, *gd_ = nullptr, *xd_ = nullptr, *act_ = nullptr, *hw_ = nullptr;
     bool capture_ = false, use_graphs_ = true;
     int cap_T_ = 0, kernels_last_ = 0;

@@ -326,9 +326,11 @@ int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float 
                             const float *qn_w, const float *kn_w, float eps, int rot_dims, const float *cos_sin_k, const float *cos_sin_v,
                             float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache, float *q_out);
 /* token t at position i = *pos0 + t sees the keys j with 0 <= i - j < window (window <= 0: every j <= i); query head h
- * reads key / value head h / (H / G); out (dt) [T][H * Dv] */
+ * reads key / value head h / (H / G); out (dt) [T][H * Dv].  scratch (ggb_window_attn_scratch_bytes, may be NULL): lets
+ * a step of few tokens spread a (token, head)'s keys over several CTAs */
+size_t ggb_window_attn_scratch_bytes(int H);
 int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
-                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out);
+                       int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out, float *scratch);
 
 /* ------------------------------------------------------------------ latent attention (csrc/latent_attention.cu)
  * The cache of a layer holds one row [c (R) | kr (Dr)] per position, ggb_latent_cache_ld(R, Dr) numbers apart, in pages

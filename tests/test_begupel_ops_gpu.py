@@ -222,7 +222,7 @@ def cos_sin(freqs, n_pos):
     return f32(np.stack([np.cos(a), np.sin(a)], -1))
 
 
-def run_window(gpu, dt, q, k, v, H, G, window, scale, fk, fv, cuts, page, qn=None, kn=None, eps=1e-5, seed=0):
+def run_window(gpu, dt, q, k, v, H, G, window, scale, fk, fv, cuts, page, qn=None, kn=None, eps=1e-5, seed=0, scratch=True):
     """feeds q, k, v rows in portions through qkv_store + window_attn over shuffled pages; returns [T, H Dv]"""
     T = q.shape[0]
     D, Dv = q.shape[1] // H, v.shape[1] // G
@@ -237,6 +237,7 @@ def run_window(gpu, dt, q, k, v, H, G, window, scale, fk, fv, cuts, page, qn=Non
     cv = dev(gpu, cos_sin(fv, T + 1)) if fv is not None else None
     rows = f32(np.concatenate([q, k, v], 1))
     ldr = rows.shape[1]
+    ws = zeros(gpu, lib.ggb_window_attn_scratch_bytes(H)) if scratch else None  # with it short steps spread over several CTAs
     lo, got = 0, []
     for c in cuts:
         xr, qo, out = dev(gpu, rows[lo:lo + c]), zeros(gpu, c * H * D * 4), zeros(gpu, c * H * Dv * es)
@@ -245,7 +246,7 @@ def run_window(gpu, dt, q, k, v, H, G, window, scale, fk, fv, cuts, page, qn=Non
         gpu.check(lib.ggb_op_window_qkv_store(dt, b, b + 4 * H * D, b + 4 * (H + G) * D, ldr, c, H, G, D, Dv, ptr(dev(gpu, f32(qn)) if qn is not None else None),
                                               ptr(dev(gpu, f32(kn)) if kn is not None else None), eps, 2 * len(fk) if fk is not None else 0, ptr(ck), ptr(cv),
                                               scale, pos0.ptr, tb.ptr, page, cache.ptr, qo.ptr), "window_qkv_store")
-        gpu.check(lib.ggb_op_window_attn(dt, qo.ptr, cache.ptr, tb.ptr, page, pos0.ptr, c, H, G, D, Dv, window or 0, ptr(cv), out.ptr), "window_attn")
+        gpu.check(lib.ggb_op_window_attn(dt, qo.ptr, cache.ptr, tb.ptr, page, pos0.ptr, c, H, G, D, Dv, window or 0, ptr(cv), out.ptr, ptr(ws)), "window_attn")
         got.append(from_dt(dt, out, (c, H * Dv)))
         lo += c
     assert lo == T
@@ -264,7 +265,7 @@ def test_window_attention_portions_and_single_tokens(gpu, dt, H, Gk, D, Dv, wind
     qn, kn = 1 + 0.2 * r.standard_normal(H * D), 1 + 0.2 * r.standard_normal(G * D)
     want = BP.window_core(BP.rms(q, 1e-5) * qn, BP.rms(k, 1e-5) * kn, v, H, G, window, 0.3, fk, fv)
     for cuts in ([T], [40] + [1] * 30 + [2, 3, 33, 42], [1] * 20 + [130]):
-        got = run_window(gpu, dt, q, k, v, H, G, window, 0.3, fk, fv, cuts, page, qn, kn)
+        got = run_window(gpu, dt, q, k, v, H, G, window, 0.3, fk, fv, cuts, page, qn, kn, scratch=len(cuts) != 21)
         assert F.rel_err(got, want) < (2e-2 if dt == BF16 else 5e-6), cuts
 
 
