@@ -166,12 +166,15 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
         for (int64_t j0 = jlo + 32 * ((int64_t)blockIdx.z * kWarps + warp); j0 <= i; j0 += step) {
             const int64_t j = j0 + lane;
             float s = -INFINITY;
+            // the lane's row of the cache, looked up once: the weighted sum below gets the other lanes' rows by shuffle
+            const int64_t jc = min(j, i);
+            const int64_t my_row = (int64_t)table[jc / B] * B + jc % B;
             if (j <= i) {
-                const E *kr = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld + koff;
+                const E *kr = cache + my_row * cache_ld + koff;
                 float a0 = 0.f, a1 = 0.f;
                 if (vec) {
                     constexpr int VN = RowVec<E>::n;
-#pragma unroll 4
+#pragma unroll 8
                     for (int d = 0; d < D; d += VN) {
                         RowVec<E> kv;
                         kv.raw = *reinterpret_cast<const uint4 *>(kr + d);
@@ -203,8 +206,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
                 for (int u = 0; u < 8; u++) {
                     const int jj = min(jb + u, n_keys - 1);
                     pj[u] = jb + u < n_keys ? __shfl_sync(0xffffffffu, p, jj) : 0.f;
-                    const int64_t jr = j0 + jj;
-                    vrow[u] = cache + ((int64_t)table[jr / B] * B + jr % B) * cache_ld + voff;
+                    vrow[u] = cache + __shfl_sync(0xffffffffu, my_row, jj) * cache_ld + voff;
                 }
 #pragma unroll
                 for (int r = 0; r < kMaxDvRegs / 2; r++) {

@@ -59,12 +59,12 @@ int paged_cache::reserve(int slot, int64_t n_tokens) {
     const size_t need = (size_t)((n_tokens + page_ - 1) / page_);
     const size_t had = s.pages.size();
     if (need <= had) return 0;
-    if (need > (size_t)n_pages_) { // a page table holds n_pages entries: trimming frees pages, not positions
-        err_ = "paged_cache: the sequence grows past the " + std::to_string((long long)n_pages_ * page_) + " positions the cache was sized for";
-        return -1;
-    }
     if (need - had > free_.size()) {
         err_ = "paged_cache: out of pages (live sequences hold more tokens than the cache was sized for)";
+        return -1;
+    }
+    if (need > (size_t)n_pages_) { // a page table holds n_pages entries: trimming frees pages, not positions
+        err_ = "paged_cache: the sequence grows past the " + std::to_string((long long)n_pages_ * page_) + " positions the cache was sized for";
         return -1;
     }
     while (s.pages.size() < need) {
