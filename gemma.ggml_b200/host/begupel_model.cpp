@@ -70,10 +70,14 @@ int bg_parse_config(const json_value &j, bg_config *c, std::string *err) {
             l.vdim = (int)m->integer("vdim", 0);
             if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0) return bad(where + "mixer sizes must be positive");
             const json_value *d = m->get("decay");
-            if (!d || d->kind != json_value::ARR || (int)d->arr.size() != l.heads) return bad(where + "'decay' must list one number per head");
-            for (const json_value &v : d->arr) {
-                if (v.kind != json_value::NUM) return bad(where + "'decay' must list numbers");
-                l.decay.push_back((float)v.num);
+            if (d && d->kind == json_value::NUM) { // one number: every head forgets at the same rate
+                l.decay.assign((size_t)l.heads, (float)d->num);
+            } else {
+                if (!d || d->kind != json_value::ARR || (int)d->arr.size() != l.heads) return bad(where + "'decay' must list one number per head");
+                for (const json_value &v : d->arr) {
+                    if (v.kind != json_value::NUM) return bad(where + "'decay' must list numbers");
+                    l.decay.push_back((float)v.num);
+                }
             }
         } else if (type == "parallel") {
             l.type = 1;
