@@ -11,7 +11,7 @@
 //   * PASS STREAM.  At create time every weight matrix is re-laid out as a stream of PASSES: one pass = two rows x
 //     one 64-block K segment (2304 B Q4_0 / 4352 B Q8_0), payloads then scales = what one consumer warp dots in one
 //     go.  A CTA's share of a phase is ONE contiguous byte range, ordered K-SEGMENT-MAJOR (segment 0 of all its row
-//     pairs, then segment 1, ...), so a trivial producer loop (lane 0 of warp 17: cp.async.bulk, SASS UBLKCP, <= 16
+//     pairs, then segment 1, ...), so a trivial producer loop (lane 0 of warp 17: cp.async.bulk, <= 16
 //     passes per ring slot, 5 slots, mbarrier completion) runs AHEAD across phase boundaries.
 //   * CONSUMERS = 16 warps.  Warp w owns pass w of every slot: 4 x LDS.128 weights, the lane's two activation
 //     blocks in registers, dp4a, the scalar reference's per-block fp32 term.  The 128 terms of a pass go to a
