@@ -3,7 +3,7 @@
 // is fp32 and lives in the caller's per-sequence block; a portion of T tokens continues from the state the previous
 // portion left and leaves its own, so a prompt may be cut anywhere.
 //
-// The two recurrences share one kernel: a CTA owns one head and a slice of CV value columns (columns are independent
+// The two recurrences share one kernel: a CTA owns one head and a slice of CV (16 or 32) value columns (columns are independent
 // in both rules), NS lanes share a column and each keeps D / NS numbers of it in registers for the whole portion.
 // Per token the lanes' partial sums meet through two shuffles.  Tokens are staged through shared memory in chunks by
 // four more warps, one chunk ahead of the recurrence; the staging pass also does what is per token and parallel:
@@ -15,8 +15,9 @@
 
 namespace {
 
-__device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
-__device__ __forceinline__ float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
+// __frcp_rn: the correctly rounded reciprocal, one instruction sequence without the slow path of the precise division
+__device__ __forceinline__ float silu_f32(float z) { return z * __frcp_rn(1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f32(float z) { return __frcp_rn(1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 // ------------------------------------------------------------------------------------------------ causal convolution
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float *__restric
 
 // ------------------------------------------------------------------------------------------------ the recurrences
 constexpr int kNS = 4;      // lanes that share a column of S
-constexpr int kCV = 32;     // value columns per CTA (kCV * kNS = 128 threads)
+constexpr int kStageWarps = 4; // warps that stage the next chunk
 constexpr int kChunk = 16;  // tokens staged at once
 
 struct rec_args {
@@ -104,27 +105,27 @@ struct rec_args {
 // MODE 0: lightning (q, k, v = silu of the raw rows; S <- decay S + k v^T; o = S^T q)
 // MODE 1: gated delta rule (unit q and k, q * D^-1/2; S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q)
 //
-// 256 threads: threads 0..127 run the recurrence on the chunk in one buffer while warps 4..7 stage the next chunk into
+// CV * 4 threads run the recurrence on the chunk in one buffer while four more warps stage the next chunk into
 // the other (global loads of a warp's four tokens in flight together), one barrier per chunk.
 // A lane's slice of a q / k row starts DS + 4 words after its neighbour's: the four 16-byte reads of a warp fall into
 // four different groups of banks (DS alone is a multiple of 8 words: all four would meet in one).
-template <int DS>
+template <int DS, int CV>
 struct rec_smem {
     static constexpr int DP = DS * kNS;        // padded D
     static constexpr int DW = (DS + 4) * kNS;  // words of a staged row
     __device__ static __forceinline__ int at(int d) { return (d / DS) * (DS + 4) + d % DS; }
     float q[kChunk][DW], k[kChunk][DW];
-    float v[kChunk][kCV], g[kChunk], beta[kChunk];
+    float v[kChunk][CV], g[kChunk], beta[kChunk];
 };
 
-template <int DS, int MODE>
-__device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, int64_t t0, int n, int h, int hk, int col0, int pw, int lane, float a_rate,
+template <int DS, int CV, int MODE>
+__device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV> &b, int64_t t0, int n, int h, int hk, int col0, int pw, int lane, float a_rate,
                                           float dtb, float q_scale) {
-    constexpr int DP = DS * kNS, PL = (DP + 31) / 32, TPW = kChunk / 4; // numbers per lane and row, tokens per producer warp
+    constexpr int DP = DS * kNS, PL = (DP + 31) / 32, TPW = kChunk / kStageWarps; // numbers per lane and row, tokens per producer warp
     float qv[TPW][PL], kv[TPW][PL], vv[TPW], bb[TPW], aa[TPW];
 #pragma unroll
     for (int u = 0; u < TPW; u++) {
-        const int tt = pw + 4 * u;
+        const int tt = pw + kStageWarps * u;
         const int64_t t = t0 + min(tt, n - 1); // past the chunk's end: the last token again, not stored
         const float *qr = p.q + t * p.ld + (int64_t)hk * p.D, *kr = p.k + t * p.ld + (int64_t)hk * p.D;
 #pragma unroll
@@ -133,7 +134,7 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, in
             qv[u][i] = d < p.D ? qr[d] : 0.f;
             kv[u][i] = d < p.D ? kr[d] : 0.f;
         }
-        vv[u] = (lane < kCV && col0 + lane < p.Dv) ? p.v[t * p.ld + (int64_t)h * p.Dv + col0 + lane] : 0.f;
+        vv[u] = (lane < CV && col0 + lane < p.Dv) ? p.v[t * p.ld + (int64_t)h * p.Dv + col0 + lane] : 0.f;
         if (MODE == 1) {
             bb[u] = p.b[t * p.ld_ba + h];
             aa[u] = p.a[t * p.ld_ba + h];
@@ -141,7 +142,7 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, in
     }
 #pragma unroll
     for (int u = 0; u < TPW; u++) {
-        const int tt = pw + 4 * u;
+        const int tt = pw + kStageWarps * u;
         if (tt >= n) continue;
         float qm = 1.f, km = 1.f;
         if (MODE == 0) {
@@ -171,22 +172,22 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS> &b, in
         for (int i = 0; i < PL; i++) {
             const int d = lane + 32 * i;
             if (d < DP) {
-                b.q[tt][rec_smem<DS>::at(d)] = qv[u][i] * qm;
-                b.k[tt][rec_smem<DS>::at(d)] = kv[u][i] * km;
+                b.q[tt][rec_smem<DS, CV>::at(d)] = qv[u][i] * qm;
+                b.k[tt][rec_smem<DS, CV>::at(d)] = kv[u][i] * km;
             }
         }
-        if (lane < kCV) b.v[tt][lane] = vv[u];
+        if (lane < CV) b.v[tt][lane] = vv[u];
     }
 }
 
-template <int DS, int MODE>
-__global__ void __launch_bounds__(2 * kCV *kNS) recurrence_kernel(rec_args p) {
+template <int DS, int CV, int MODE>
+__global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(rec_args p) {
     extern __shared__ __align__(16) unsigned char rec_raw[];
-    rec_smem<DS> *buf = reinterpret_cast<rec_smem<DS> *>(rec_raw);
-    const int h = blockIdx.x, col0 = blockIdx.y * kCV;
+    rec_smem<DS, CV> *buf = reinterpret_cast<rec_smem<DS, CV> *>(rec_raw);
+    const int h = blockIdx.x, col0 = blockIdx.y * CV;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool producer = warp >= (kCV * kNS) / 32;
-    const int s = tid % kNS, cl = (tid / kNS) % kCV, col = col0 + cl;
+    const bool producer = warp >= (CV * kNS) / 32;
+    const int s = tid % kNS, cl = (tid / kNS) % CV, col = col0 + cl;
     const bool live = !producer && col < p.Dv;
     const int hk = MODE == 1 ? h / (p.H / p.G) : h; // the q / k head this head reads
     float S[DS];
@@ -199,17 +200,17 @@ __global__ void __launch_bounds__(2 * kCV *kNS) recurrence_kernel(rec_args p) {
     const float decay = MODE == 0 ? p.decay[h] : 0.f;
     const float a_rate = MODE == 1 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
     const float q_scale = 1.0f / sqrtf((float)p.D);
-    const int pw = warp - (kCV * kNS) / 32;
-    if (producer) rec_stage<DS, MODE>(p, buf[0], 0, (int)min((int64_t)kChunk, p.T), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
+    const int pw = warp - (CV * kNS) / 32;
+    if (producer) rec_stage<DS, CV, MODE>(p, buf[0], 0, (int)min((int64_t)kChunk, p.T), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
     __syncthreads();
     int cur = 0;
     for (int64_t t0 = 0; t0 < p.T; t0 += kChunk, cur ^= 1) {
         const int n = (int)min((int64_t)kChunk, p.T - t0);
         if (producer) {
             if (t0 + kChunk < p.T)
-                rec_stage<DS, MODE>(p, buf[cur ^ 1], t0 + kChunk, (int)min((int64_t)kChunk, p.T - t0 - kChunk), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
+                rec_stage<DS, CV, MODE>(p, buf[cur ^ 1], t0 + kChunk, (int)min((int64_t)kChunk, p.T - t0 - kChunk), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
         } else {
-            const rec_smem<DS> &b = buf[cur];
+            const rec_smem<DS, CV> &b = buf[cur];
             for (int tt = 0; tt < n; tt++) {
                 const float4 *k4 = reinterpret_cast<const float4 *>(&b.k[tt][s * (DS + 4)]);
                 const float4 *q4 = reinterpret_cast<const float4 *>(&b.q[tt][s * (DS + 4)]);
@@ -275,15 +276,23 @@ __global__ void __launch_bounds__(2 * kCV *kNS) recurrence_kernel(rec_args p) {
     }
 }
 
-template <int DS, int MODE>
-int recurrence_launch_ds(const rec_args &p) {
-    const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + kCV - 1) / kCV));
-    const size_t smem = 2 * sizeof(rec_smem<DS>);
-    auto k = recurrence_kernel<DS, MODE>;
+template <int DS, int CV, int MODE>
+int recurrence_launch_cv(const rec_args &p) {
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + CV - 1) / CV));
+    const size_t smem = 2 * sizeof(rec_smem<DS, CV>);
+    auto k = recurrence_kernel<DS, CV, MODE>;
     if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<grid, 2 * kCV * kNS, smem, ggb_cuda_stream()>>>(p);
+    k<<<grid, CV * kNS + 32 * kStageWarps, smem, ggb_cuda_stream()>>>(p);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
+}
+
+// value columns per CTA: 16 while that leaves a CTA per SM at most (the kernel is bound by instruction issue of the one
+// CTA an SM holds, so more SMs per head is what helps), else 32
+template <int DS, int MODE>
+int recurrence_launch_ds(const rec_args &p) {
+    if ((int64_t)p.H * ((p.Dv + 15) / 16) <= ggb_sm_count()) return recurrence_launch_cv<DS, 16, MODE>(p);
+    return recurrence_launch_cv<DS, 32, MODE>(p);
 }
 
 template <int MODE>

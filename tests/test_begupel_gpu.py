@@ -137,8 +137,8 @@ OTHER = {
     "one_key_head": lambda: F.config([F.parallel(F.left(heads=6, kv_heads=1, dim=10, vdim=4, window=1, base=0), F.right(heads=3, kv_heads=1, dim=9, vdim=11, conv=8), mlp=7)],
                                      vocab=30, width=22, groups=2, taps=8, buckets=1),
     "only_lightning": lambda: F.config([F.lightning(heads=2, dim=6, vdim=12), F.lightning(heads=4, dim=5, vdim=3, mlp=11)], vocab=19, width=20, groups=5, taps=3, buckets=3),
-    "only_parallel": lambda: F.config([F.parallel(mlp=None), F.parallel(F.left(heads=1, kv_heads=1, dim=2, vdim=2, window=200, dims=2), F.right(heads=1, kv_heads=1, dim=3, vdim=1, conv=5))],
-                                      vocab=64, width=8, groups=2, taps=2),
+    "only_parallel": lambda: F.config([F.parallel(mlp=None), F.parallel(F.left(heads=1, kv_heads=1, dim=4, vdim=2, window=200, dims=2), F.right(heads=1, kv_heads=1, dim=3, vdim=1, conv=5))],
+                                      vocab=64, width=12, groups=2, taps=2),
     "wide": lambda: F.config([F.lightning(heads=2, dim=64, vdim=32, mlp=96), F.parallel(F.left(heads=4, kv_heads=2, dim=32, vdim=64, window=70, dims=16, factor=None),
                                                                                          F.right(heads=4, kv_heads=2, dim=128, vdim=48, conv=4), mlp=160),
                               F.parallel(F.left(heads=2, kv_heads=1, dim=64, vdim=34, window=9), F.right(heads=1, kv_heads=1, dim=20, vdim=70, conv=2), mlp=None)],
